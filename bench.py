@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the KDA forward pass (tokens/s; one "step" = one forward over the workload).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg4] [--algo auto]
+
+N > 1 is launched with torch.distributed.run (one rank per GPU); every rank processes its own
+copy of the per-GPU workload (sequences are independent: no data-path collective, weak
+scaling).  Rank 0 prints ONE JSON line.
+
+  value    whole-job tokens/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e      the same through the host-buffer API: pinned host inputs -> H2D -> forward -> D2H
+  roofline dominant kernel: algorithmic bytes / its measured launch time vs measured HBM peak
+  cpu_baseline  the CPU oracle (a port of the reference's torch_ref numerics) on a bounded sample
+
+--impl reference times the CPU oracle alone (the reference has no CPU implementation of its
+own; its torch_ref needs a GPU), with all host threads, on a bounded sample of the workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "kda_fwd_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def config_dict(w, algo):
+    """The workload description both arms print."""
+    from flashkda_b200.synth import algorithmic_bytes
+    return {"workload": w.name, "B_per_gpu": w.B, "T": w.T, "H": w.H, "K": 128, "V": 128, "chunk": 16,
+            "lower_bound": w.lower_bound, "state": w.state_out or w.state_in or "none",
+            "varlen_sequences": w.n_seqs if w.seq_lens else 0, "algo": algo,
+            "l2_policy": "inputs exceed L2 (%.1f GB per step)" % (algorithmic_bytes(w) / 1e9),
+            "sharding": "independent sequences per GPU, no collective"}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg4")
+    ap.add_argument("--algo", default=None)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target duration of the CPU baseline sample")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------
+# clocks: sample nvidia-smi during the timed region
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU oracle timing (cpu_baseline leg and the --impl reference arm)
+# ------------------------------------------------------------------------------------------
+def cpu_sample_workload(w, target_seconds):
+    """A bounded sample of workload ``w``: one sequence, all H heads, same gate bound and state
+    options, with T chosen so that the oracle runs for about ``target_seconds``."""
+    import torch
+    import oracle
+    from flashkda_b200.synth import Workload, make_inputs
+    probe = Workload("probe", 1, 256, w.H, lower_bound=w.lower_bound, state_in=w.state_in, state_out=w.state_out)
+    inp = make_inputs(probe)
+    t0 = time.perf_counter()
+    oracle.fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"], inp["A_log"],
+               inp["dt_bias"], inp["lower_bound"], inp["initial_state"], inp["final_state"], None)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    T = int(256 * target_seconds / dt) // 16 * 16
+    T = max(256, min(T, w.T))
+    return Workload(f"{w.name}-cpu-sample", 1, T, w.H, lower_bound=w.lower_bound, state_in=w.state_in,
+                    state_out=w.state_out)
+
+
+def time_oracle(sample, steps, warmup):
+    import oracle
+    from flashkda_b200.synth import make_inputs
+    inp = make_inputs(sample)
+    args = (inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"], inp["A_log"],
+            inp["dt_bias"], inp["lower_bound"], inp["initial_state"], inp["final_state"], None)
+    for _ in range(warmup):
+        oracle.fwd(*args)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.fwd(*args)
+    dt = (time.perf_counter() - t0) / steps
+    return sample.tokens / dt, dt
+
+
+def run_reference_arm(a):
+    """The CPU arm: oracle port of the reference numerics, all host threads, bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import flashkda_b200
+    import oracle
+    from flashkda_b200.synth import config
+    w = config(a.workload)
+    total_budget = 120.0  # seconds for the whole steps+warmup run
+    per_step = max(0.5, min(a.cpu_seconds, total_budget / max(1, a.steps + a.warmup)))
+    sample = cpu_sample_workload(w, per_step)
+    tps, dt = time_oracle(sample, a.steps, a.warmup)
+    cores = oracle.num_threads()
+    desc = f"1 sequence x T={sample.T} x H={sample.H} of {w.name} (B={w.B}, T={w.T}, H={w.H})"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_dict(w, a.algo or flashkda_b200.default_algo()),
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+    import flashkda_b200
+    from flashkda_b200 import _lib
+    from flashkda_b200.host import fwd_host
+    from flashkda_b200.synth import (algorithmic_bytes, algorithmic_flops, config, make_inputs)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = config(a.workload)
+    inp = make_inputs(w, device=dev, seed=rank)
+    algo = a.algo or flashkda_b200.default_algo()
+    ws_bytes = flashkda_b200.get_workspace_size(w.tokens, w.H, w.n_seqs, algo=algo)
+    workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+
+    def step(phase_mask=0):
+        flashkda_b200.fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
+                          A_log=inp["A_log"], dt_bias=inp["dt_bias"], lower_bound=inp["lower_bound"],
+                          initial_state=inp["initial_state"], final_state=inp["final_state"],
+                          cu_seqlens=inp["cu_seqlens"], algo=algo, workspace=workspace, phase_mask=phase_mask)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(a.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    barrier()
+    launches_per_step = flashkda_b200.last_launch_count()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / a.steps
+    value = world * w.tokens / (ms_step * 1e-3)
+
+    # ---- dominant kernel alone (CUDA events on the launching stream) ----
+    kernel_name, kernel_ms = "fkda::recurrence_kernel", None
+    n_phase = 3
+    barrier()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    step(_lib.PHASE_RECURRENCE)
+    torch.cuda.synchronize(dev)
+    p0.record()
+    for _ in range(n_phase):
+        step(_lib.PHASE_RECURRENCE)
+    p1.record()
+    torch.cuda.synchronize(dev)
+    kernel_ms = p0.elapsed_time(p1) / n_phase
+    step()  # leave the workspace and outputs consistent
+    torch.cuda.synchronize(dev)
+
+    # ---- end to end through the host-buffer API ----
+    e2e = None
+    if not a.no_e2e:
+        e2e = measure_e2e(a, w, inp, dev, world, algo, fwd_host)
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak_gbs, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak_gbs, peak_src = 6650.0, "fallback"
+    alg_bytes = algorithmic_bytes(w)
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get(f"{algo}:{w.name}")
+
+    cpu = None
+    if not a.no_cpu and world == 1:
+        import oracle
+        sample = cpu_sample_workload(w, a.cpu_seconds)
+        tps, dt = time_oracle(sample, 1, 0)
+        cpu = {"value": tps, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"1 sequence x T={sample.T} x H={sample.H} of {w.name}, {dt:.1f} s"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": config_dict(w, algo),
+        "tflops": world * algorithmic_flops(w) / (ms_step * 1e-3) / 1e12,
+        "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
+                     "frac": achieved / peak_gbs, "peak_source": peak_src, "traffic": traffic,
+                     "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": alg_bytes,
+                     "whole_forward_frac": alg_bytes / (ms_step * 1e-3) / 1e9 / peak_gbs},
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * a.steps, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_e2e(a, w, inp, dev, world, algo, fwd_host):
+    """Pinned host buffers -> device -> forward -> host, every step, through fwd_host."""
+    import torch
+    import torch.distributed as dist
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = 0
+    names = ("q", "k", "v", "g", "beta", "out", "initial_state", "final_state")
+    need = sum(inp[n].numel() * inp[n].element_size() for n in names if inp[n] is not None)
+    if avail < 2.5 * need * world:
+        return {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "skipped": f"host memory too small to pin {need * world / 1e9:.1f} GB"}
+    host = {}
+    for n in names:
+        if inp[n] is None:
+            host[n] = None
+            continue
+        host[n] = torch.empty(inp[n].shape, dtype=inp[n].dtype, pin_memory=True)
+        host[n].copy_(inp[n])
+    A_h, dt_h = inp["A_log"].cpu().pin_memory(), inp["dt_bias"].cpu().pin_memory()
+    cu_h = None if inp["cu_seqlens"] is None else inp["cu_seqlens"].cpu().pin_memory()
+    torch.cuda.synchronize(dev)
+
+    def one():
+        return fwd_host(host["q"], host["k"], host["v"], host["g"], host["beta"], inp["scale"], host["out"], A_h,
+                        dt_h, inp["lower_bound"], host["initial_state"], host["final_state"], cu_h, device=dev,
+                        slab_sequences=1, algo=algo)
+
+    one()  # warm-up (also allocates the staging buffers in the caching allocator)
+    steps = max(1, min(a.steps, 3))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        h2d, d2h = one()  # returns after its own copy streams have been joined and synchronised
+    ev1.record()
+    torch.cuda.synchronize(dev)
+    dt = ev0.elapsed_time(ev1) * 1e-3 / steps
+    t = torch.tensor([dt], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt = float(t.item())
+    del host
+    return {"value": world * w.tokens / dt, "unit": UNIT, "h2d_bytes_per_step": int(h2d) * world,
+            "d2h_bytes_per_step": int(d2h) * world, "ms_per_step": dt * 1e3, "steps": steps,
+            "api": "flashkda_b200.host.fwd_host (pinned host tensors, per-sequence slabs, copy/compute overlap)"}
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        run_reference_arm(a)
+    else:
+        run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

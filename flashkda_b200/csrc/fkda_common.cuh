@@ -1,0 +1,190 @@
+// Shared device helpers for the KDA forward kernels (sm_100a).
+//
+// The numerics follow the reference's executable contract (tests/torch_ref.py:124-251
+// and the device helpers csrc/smxx/utils.cuh:38-59): the same approximate PTX
+// transcendentals, one bf16 rounding after every element-wise bf16 operation, fp32
+// accumulation in contractions, fp16 in the 16x16 inverse.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fkda {
+
+constexpr int kD = 128;     // K = V
+constexpr int kChunk = 16;  // tokens per recurrence step
+
+// Bytes of one (head, chunk) record in the two-pass workspace:
+// kd, qd, kr [16,128] bf16; E_tot [128] f32; INV, Mqk [16,16] bf16.
+constexpr int kWsKd = 0;
+constexpr int kWsQd = kWsKd + kChunk * kD * 2;
+constexpr int kWsKr = kWsQd + kChunk * kD * 2;
+constexpr int kWsEt = kWsKr + kChunk * kD * 2;
+constexpr int kWsInv = kWsEt + kD * 4;
+constexpr int kWsMqk = kWsInv + kChunk * kChunk * 2;
+constexpr int kWsRecord = kWsMqk + kChunk * kChunk * 2;  // 13824
+static_assert(kWsRecord == 13824, "workspace record size");
+
+// ---- approximate transcendentals: the instructions are part of the contract ----
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float rsqrt_approx(float x) {
+    float r;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+// sigmoid(x) = tanh(x/2)/2 + 1/2  (csrc/smxx/utils.cuh:50-53)
+__device__ __forceinline__ float sigmoid_tanh(float x) {
+    float th = tanh_approx(x * 0.5f);
+    return __fmaf_rn(th, 0.5f, 0.5f);
+}
+
+// ---- bf16 helpers: every op rounds to nearest-even once ----
+__device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ __nv_bfloat16 f2bf(float x) { return __float2bfloat16_rn(x); }
+__device__ __forceinline__ __nv_bfloat16 bfmul(__nv_bfloat16 a, __nv_bfloat16 b) { return f2bf(bf2f(a) * bf2f(b)); }
+__device__ __forceinline__ __nv_bfloat16 bfadd(__nv_bfloat16 a, __nv_bfloat16 b) { return f2bf(bf2f(a) + bf2f(b)); }
+__device__ __forceinline__ __nv_bfloat16 bfsub(__nv_bfloat16 a, __nv_bfloat16 b) { return f2bf(bf2f(a) - bf2f(b)); }
+
+__device__ __forceinline__ float bfbits2f(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
+__device__ __forceinline__ float bf_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- warp-level mma.sync m16n8k16, fp16 operands AND fp16 accumulators ----
+// (the instruction the reference's inverse uses: csrc/smxx/utils.cuh:199-260)
+__device__ __forceinline__ void mma_f16_f16acc(uint32_t& d0, uint32_t& d1, uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1, uint32_t c0, uint32_t c1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0,%1}, {%2,%3,%4,%5}, {%6,%7}, {%8,%9};\n"
+        : "=r"(d0), "=r"(d1)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
+}
+// bf16 operands, fp32 accumulators
+__device__ __forceinline__ void mma_bf16_f32acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
+    __half2 x = *reinterpret_cast<__half2*>(&a), y = *reinterpret_cast<__half2*>(&b);
+    __half2 z = __hadd2(x, y);
+    return *reinterpret_cast<uint32_t*>(&z);
+}
+
+// 16x16 fp16 product C = A * B by one warp, all three row-major in shared memory with
+// row pitch `ld` halves (ld even).  Fragments are fetched with plain 32/16-bit loads.
+// A-fragment of row-major X: regs {X[g][2t..], X[g+8][2t..], X[g][2t+8..], X[g+8][2t+8..]}.
+struct Frag16 {
+    uint32_t r[4];
+};
+__device__ __forceinline__ Frag16 load_a_frag_h(const __half* X, int ld, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    Frag16 f;
+    f.r[0] = *reinterpret_cast<const uint32_t*>(X + g * ld + 2 * t);
+    f.r[1] = *reinterpret_cast<const uint32_t*>(X + (g + 8) * ld + 2 * t);
+    f.r[2] = *reinterpret_cast<const uint32_t*>(X + g * ld + 2 * t + 8);
+    f.r[3] = *reinterpret_cast<const uint32_t*>(X + (g + 8) * ld + 2 * t + 8);
+    return f;
+}
+// B-fragments (both n-halves) of row-major Y[k][n]: reg pairs {Y[2t][n],Y[2t+1][n]}, {Y[2t+8][n],Y[2t+9][n]}
+// for n = g (regs 0,1) and n = g + 8 (regs 2,3).
+__device__ __forceinline__ Frag16 load_b_frag_h(const __half* Y, int ld, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    auto pk = [&](int k, int n) {
+        __half2 v = __halves2half2(Y[k * ld + n], Y[(k + 1) * ld + n]);
+        return *reinterpret_cast<uint32_t*>(&v);
+    };
+    Frag16 f;
+    f.r[0] = pk(2 * t, g);
+    f.r[1] = pk(2 * t + 8, g);
+    f.r[2] = pk(2 * t, g + 8);
+    f.r[3] = pk(2 * t + 8, g + 8);
+    return f;
+}
+// C-fragment layout (fp16 accumulators): regs {C[g][2t..], C[g+8][2t..]} for columns 0-7,
+// then the same for columns 8-15.
+__device__ __forceinline__ void store_c_frag_h(__half* Z, int ld, int lane, const Frag16& c) {
+    const int g = lane >> 2, t = lane & 3;
+    *reinterpret_cast<uint32_t*>(Z + g * ld + 2 * t) = c.r[0];
+    *reinterpret_cast<uint32_t*>(Z + (g + 8) * ld + 2 * t) = c.r[1];
+    *reinterpret_cast<uint32_t*>(Z + g * ld + 2 * t + 8) = c.r[2];
+    *reinterpret_cast<uint32_t*>(Z + (g + 8) * ld + 2 * t + 8) = c.r[3];
+}
+__device__ __forceinline__ Frag16 mma16x16_h(const Frag16& a, const Frag16& b) {
+    Frag16 c;
+    mma_f16_f16acc(c.r[0], c.r[1], a.r[0], a.r[1], a.r[2], a.r[3], b.r[0], b.r[1], 0u, 0u);
+    mma_f16_f16acc(c.r[2], c.r[3], a.r[0], a.r[1], a.r[2], a.r[3], b.r[2], b.r[3], 0u, 0u);
+    return c;
+}
+
+// Inverse of the unit lower-triangular (I + L), L strictly lower 16x16 fp16, by one warp:
+//   (I + L)^-1 = (I - L)(I + L^2)(I + L^4)(I + L^8)
+// with fp16 products/accumulators and fp16 additions, result rounded to bf16
+// (csrc/smxx/utils.cuh:262-311; tests/torch_ref.py:221-229).
+// Ls: L (row-major, pitch ld); Ws: scratch 16 x ld halves; inv_out: bf16 [16][16] dense.
+// Both Ls and Ws are clobbered.  All 32 lanes of the warp must call.
+__device__ __forceinline__ void neumann_inverse_warp(__half* Ls, __half* Ws, int ld, __nv_bfloat16* inv_out,
+                                                     int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    // INV0 = I - L in C-fragment coordinates
+    Frag16 inv_c;
+    {
+        auto el = [&](int r, int c) {
+            __half x = Ls[r * ld + c];
+            return (r == c) ? __hsub(__float2half_rn(1.0f), x) : __hneg(x);
+        };
+        auto pk = [&](int r, int c) {
+            __half2 v = __halves2half2(el(r, c), el(r, c + 1));
+            return *reinterpret_cast<uint32_t*>(&v);
+        };
+        inv_c.r[0] = pk(g, 2 * t);
+        inv_c.r[1] = pk(g + 8, 2 * t);
+        inv_c.r[2] = pk(g, 2 * t + 8);
+        inv_c.r[3] = pk(g + 8, 2 * t + 8);
+    }
+    // A-fragment and C-fragment register layouts coincide for a 16x16 row-major matrix
+    // (regs: [g][2t], [g+8][2t], [g][2t+8], [g+8][2t+8]), so INV can be reused as A directly.
+    Frag16 pow_a = load_a_frag_h(Ls, ld, lane);  // L
+    Frag16 pow_b = load_b_frag_h(Ls, ld, lane);
+    __syncwarp();
+#pragma unroll
+    for (int step = 0; step < 3; ++step) {
+        Frag16 p2 = mma16x16_h(pow_a, pow_b);  // L^(2^(step+1))
+        store_c_frag_h(Ws, ld, lane, p2);
+        __syncwarp();
+        pow_b = load_b_frag_h(Ws, ld, lane);
+        pow_a = p2;
+        __syncwarp();
+        Frag16 m = mma16x16_h(inv_c, pow_b);  // INV * L^(2^(step+1))
+#pragma unroll
+        for (int i = 0; i < 4; ++i) inv_c.r[i] = hadd2_u32(inv_c.r[i], m.r[i]);
+    }
+    auto st = [&](int r, int c, uint32_t packed) {
+        __half2 h = *reinterpret_cast<__half2*>(&packed);
+        float2 f = __half22float2(h);
+        *reinterpret_cast<uint32_t*>(inv_out + r * kChunk + c) = pack_bf2(f.x, f.y);
+    };
+    st(g, 2 * t, inv_c.r[0]);
+    st(g + 8, 2 * t, inv_c.r[1]);
+    st(g, 2 * t + 8, inv_c.r[2]);
+    st(g + 8, 2 * t + 8, inv_c.r[3]);
+}
+
+}  // namespace fkda

@@ -1,0 +1,106 @@
+/*
+ * flashkda_b200 — C ABI of the B200 (sm_100a) Kimi Delta Attention forward.
+ *
+ * Plain pointers and sizes only; every pointer is DEVICE memory unless stated
+ * otherwise.  All entry points enqueue work on the CUDA stream they are given
+ * and return without synchronising (the contract of the reference operator,
+ * csrc/flash_kda.cpp:136).  A return value of 0 means success; any other value
+ * is one of the FKDA_ERR_* codes (fkda_status_string() names them).
+ *
+ * Reference interfaces replaced (paths within the reference project):
+ *   fkda_fwd              <- fwd(...)               csrc/flash_kda.cpp:28-217
+ *                            launch_fwd<...>(...)   csrc/fwd.h:6-27
+ *   fkda_workspace_bytes  <- get_workspace_size()   csrc/flash_kda.cpp:5-26
+ */
+#ifndef FLASHKDA_B200_H_
+#define FLASHKDA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FKDA_HEAD_DIM 128 /* K = V = 128 (csrc/flash_kda.cpp:110) */
+#define FKDA_CHUNK 16     /* tokens per recurrence step (csrc/flash_kda.cpp:138) */
+
+enum {
+    FKDA_OK = 0,
+    FKDA_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+    FKDA_ERR_BAD_SHAPE = 2,      /* B, T, H, N or a stride is out of range */
+    FKDA_ERR_BAD_STATE_DTYPE = 3,
+    FKDA_ERR_VARLEN_BATCH = 4,   /* cu_seqlens given but B != 1 */
+    FKDA_ERR_WORKSPACE = 5,      /* workspace missing or too small */
+    FKDA_ERR_BAD_ALGO = 6,
+    FKDA_ERR_LAUNCH = 7,         /* a kernel launch or CUDA runtime call failed */
+    FKDA_ERR_ALIGNMENT = 8,      /* a tensor base address or stride is not 16-byte aligned */
+    FKDA_ERR_DEVICE_STATUS = 9   /* a kernel gave up on a bounded internal wait */
+};
+
+enum { FKDA_STATE_BF16 = 0, FKDA_STATE_FP32 = 1 };
+
+enum { FKDA_PHASE_PREPARE = 1, FKDA_PHASE_RECURRENCE = 2 };
+
+/* Which device implementation runs. */
+enum {
+    FKDA_ALGO_AUTO = 0,
+    FKDA_ALGO_TWOPASS = 1 /* prepare kernel -> HBM workspace -> recurrence kernel (CUDA cores) */
+};
+
+/*
+ * Arguments of one forward call; mirrors flash_kda.fwd (flash_kda/__init__.py:5).
+ * Token-major tensors are addressed as
+ *     x[token][head][d]  at  x + token * token_stride + head * 128 + d     (bf16 elements)
+ *     beta[token][head]  at  beta + token * beta_token_stride + head
+ * with token = b * T + t.  Dense tensors use token_stride = H * 128 and
+ * beta_token_stride = H; a larger stride addresses a head-slice of a wider tensor
+ * without a copy.  States are dense [N, H, 128 (V), 128 (K)].
+ */
+typedef struct fkda_fwd_params {
+    const void* q;             /* bf16 */
+    const void* k;             /* bf16 */
+    const void* v;             /* bf16 */
+    const void* g;             /* bf16, gate before activation */
+    const void* beta;          /* bf16, beta logits */
+    void* out;                 /* bf16, written in place */
+    const float* A_log;        /* [H] */
+    const float* dt_bias;      /* [H, 128] */
+    const void* initial_state; /* NULL = start from zero */
+    void* final_state;         /* NULL = not exported */
+    int32_t state_dtype;       /* FKDA_STATE_*: dtype of whichever states are given */
+    int32_t algo;              /* FKDA_ALGO_* */
+    const int64_t* cu_seqlens; /* [N + 1] device int64, or NULL for B sequences of length T */
+    int64_t B, T, H, N;        /* N = number of sequences (= B when cu_seqlens is NULL) */
+    int64_t token_stride;      /* elements between consecutive tokens of q/k/v/g/out */
+    int64_t beta_token_stride; /* elements between consecutive tokens of beta */
+    float scale;
+    double lower_bound;        /* gate lower bound, -5 <= lower_bound <= 0 */
+    void* workspace;           /* >= fkda_workspace_bytes(B*T, H, N, algo) bytes, 256-byte aligned */
+    size_t workspace_bytes;
+    int32_t phase_mask;        /* measurement aid for multi-kernel algos: 0 = whole forward; otherwise a
+                                  bit set of FKDA_PHASE_* to launch (the workspace must then already hold
+                                  what the skipped phases produce) */
+    int32_t reserved;
+} fkda_fwd_params;
+
+/* Scratch bytes one call needs (0 is a valid answer).  Replaces get_workspace_size
+ * (csrc/flash_kda.cpp:5-26): same arguments plus the implementation selector. */
+size_t fkda_workspace_bytes(int64_t T_total, int64_t H, int64_t N, int32_t algo);
+
+/* Enqueues the forward pass on `stream` (a cudaStream_t passed as void*). */
+int fkda_fwd(const fkda_fwd_params* p, void* stream);
+
+/* Library ABI version (major * 1000 + minor). */
+int fkda_version(void);
+
+/* Static, human-readable name of a status code. */
+const char* fkda_status_string(int status);
+
+/* Number of kernels the last successful fkda_fwd call on this thread launched. */
+int fkda_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHKDA_B200_H_ */

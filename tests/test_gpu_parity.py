@@ -1,0 +1,205 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle and the
+committed golden fixtures.
+
+Tolerances.  The target states: out within max-abs 2e-2, final_state within 1e-3 relative
+(RMSE ratio, reference tests/test_fwd.py:13-16) against the reference's GPU results.  The CPU
+oracle and the fixtures use exact tanh/exp2 where the GPU uses tanh.approx / ex2.approx, which
+moves results by a few 1e-3 relative; the bounds against them are therefore out max-abs 2e-2,
+out ratio 1e-2 and state ratio 1e-2.  Bit-exact equalities are asserted wherever both sides ran
+on the GPU (chaining, batching, varlen-vs-fixed, implementation-vs-implementation).
+"""
+import pytest
+import torch
+
+import flashkda_b200
+import oracle
+from flashkda_b200.synth import Workload, config, make_inputs, make_reference_test_inputs, to_device
+from kda_testlib import GOLDEN_CASES, load_golden, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+OUT_MAX_ABS = 2e-2
+OUT_RATIO = 1e-2
+STATE_RATIO = 1e-2
+
+
+def run_gpu(inp, algo=None):
+    d = to_device(inp, "cuda")
+    flashkda_b200.fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["out"], A_log=d["A_log"],
+                      dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], initial_state=d["initial_state"],
+                      final_state=d["final_state"], cu_seqlens=d["cu_seqlens"], algo=algo)
+    torch.cuda.synchronize()
+    assert flashkda_b200.last_launch_count() > 0
+    return d["out"].cpu(), None if d["final_state"] is None else d["final_state"].cpu()
+
+
+def check_against(out, hT, ref_out, ref_hT):
+    assert torch.isfinite(out.float()).all()
+    assert oracle.max_abs(ref_out, out) <= OUT_MAX_ABS
+    assert oracle.err_ratio(ref_out, out) <= OUT_RATIO
+    if ref_hT is not None:
+        assert hT is not None and torch.isfinite(hT.float()).all()
+        assert oracle.err_ratio(ref_hT.float(), hT.float()) <= STATE_RATIO
+        # every exported state value is bf16-representable (reference: csrc/smxx/utils.cuh:377-378)
+        assert torch.equal(hT.to(torch.bfloat16).to(hT.dtype), hT)
+
+
+@pytest.mark.parametrize("name", list(GOLDEN_CASES))
+def test_golden_fixtures(name):
+    w, inp, gold_out, gold_hT = load_golden(name)
+    out, hT = run_gpu(inp)
+    check_against(out, hT, gold_out, gold_hT)
+
+
+STATE_IO = [("in+out", True, True), ("in_only", True, False), ("out_only", False, True), ("none", False, False)]
+
+
+# shape lists of the reference's full matrix (tests/test_fwd_full.py:58-59), sizes the oracle
+# finishes in well under a second
+@pytest.mark.parametrize("T", [16, 64, 256, 1024, 17, 37, 97])
+@pytest.mark.parametrize("H", [1, 4])
+@pytest.mark.parametrize("state_dtype", ["bf16", "fp32"])
+@pytest.mark.parametrize("io", STATE_IO, ids=[s[0] for s in STATE_IO])
+def test_fixed_matrix(T, H, state_dtype, io):
+    _, has_in, has_out = io
+    w = Workload("m", 1, T, H, state_in=state_dtype if has_in else None, state_out=state_dtype if has_out else None)
+    inp = make_reference_test_inputs(w)
+    if has_in:  # arange-valued states are huge; scale to a realistic magnitude for a relative test
+        inp["initial_state"] = (inp["initial_state"].float() % 7.0 * 0.01).to(inp["initial_state"].dtype)
+    ref_out, ref_hT = run_oracle(inp)
+    out, hT = run_gpu(inp)
+    check_against(out, hT, ref_out, ref_hT)
+
+
+VARLEN = [[16], [16, 16], [4, 8, 12], [64, 128, 256], [1300, 547, 2048, 963, 271, 3063], [1024] * 8, [20, 50, 100],
+          [17, 33, 65], [1, 1, 1, 5, 1], [0, 31, 0, 16, 0]]
+
+
+@pytest.mark.parametrize("lens", VARLEN, ids=[str(i) for i in range(len(VARLEN))])
+@pytest.mark.parametrize("H", [1, 4])
+@pytest.mark.parametrize("state_dtype", ["bf16", "fp32"])
+def test_varlen_matrix(lens, H, state_dtype):
+    w = Workload("v", 1, sum(lens), H, state_in=state_dtype, state_out=state_dtype, seq_lens=lens)
+    inp = make_inputs(w, seed=1)
+    ref_out, ref_hT = run_oracle(inp)
+    out, hT = run_gpu(inp)
+    check_against(out, hT, ref_out, ref_hT)
+    # zero-length sequences pass the (bf16-rounded) state through untouched
+    for n, L in enumerate(lens):
+        if L == 0:
+            assert torch.equal(hT[n].float(), inp["initial_state"][n].to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("B,T", [(2, 64), (2, 1024), (4, 256), (8, 128)])
+def test_batched(B, T):
+    w = Workload("b", B, T, 4, state_in="fp32", state_out="fp32")
+    inp = make_inputs(w, seed=2)
+    ref_out, ref_hT = run_oracle(inp)
+    out, hT = run_gpu(inp)
+    check_against(out, hT, ref_out, ref_hT)
+
+
+def test_cfg1_named_configuration():
+    inp = make_inputs(config("cfg1"))
+    ref_out, ref_hT = run_oracle(inp)
+    out, hT = run_gpu(inp)
+    check_against(out, hT, ref_out, ref_hT)
+
+
+def test_gate_stress_cases():
+    """Gate/bias sweep in the style of the reference's accuracy test (tests/test_fwd.py:45-68)."""
+    w = Workload("g", 1, 256, 2, state_out="fp32")
+    for gval, bias in [(-8.0, 0.0), (-4.0, 0.0), (0.0, 0.0), (8.0, 0.0), (0.0, 4.0), (0.0, -8.0)]:
+        inp = make_reference_test_inputs(w, seed=7)
+        inp["g"] = torch.full_like(inp["g"], gval)
+        inp["dt_bias"] = torch.full_like(inp["dt_bias"], bias)
+        ref_out, ref_hT = run_oracle(inp)
+        out, hT = run_gpu(inp)
+        check_against(out, hT, ref_out, ref_hT)
+
+
+# ---- size-independent properties, GPU against GPU: bit-exact ----
+
+def test_chained_calls_equal_one_shot():
+    w = Workload("c", 1, 4096, 8, state_in="bf16", state_out="bf16")
+    inp = make_inputs(w, seed=3)
+    out_full, hT_full = run_gpu(inp)
+    cut = 1648  # multiple of 16
+    a, b = dict(inp), dict(inp)
+    for key in ("q", "k", "v", "g", "beta"):
+        a[key] = inp[key][:, :cut].contiguous()
+        b[key] = inp[key][:, cut:].contiguous()
+    a["out"], b["out"] = torch.zeros_like(a["v"]), torch.zeros_like(b["v"])
+    out_a, hT_a = run_gpu(a)
+    b["initial_state"] = hT_a
+    out_b, hT_b = run_gpu(b)
+    assert torch.equal(torch.cat([out_a, out_b], dim=1), out_full)
+    assert torch.equal(hT_b, hT_full)
+
+
+def test_varlen_equals_separate_fixed_calls():
+    lens = [300, 17, 1, 512, 100]
+    w = Workload("vf", 1, sum(lens), 4, state_in="fp32", state_out="fp32", seq_lens=lens)
+    inp = make_inputs(w, seed=4)
+    out, hT = run_gpu(inp)
+    pos = 0
+    for n, L in enumerate(lens):
+        one = dict(inp)
+        for key in ("q", "k", "v", "g", "beta"):
+            one[key] = inp[key][:, pos:pos + L].contiguous()
+        one["out"] = torch.zeros_like(one["v"])
+        one["initial_state"] = inp["initial_state"][n:n + 1].contiguous()
+        one["final_state"] = torch.zeros_like(one["initial_state"])
+        one["cu_seqlens"] = None
+        o1, h1 = run_gpu(one)
+        assert torch.equal(o1[0], out[0, pos:pos + L])
+        assert torch.equal(h1[0], hT[n])
+        pos += L
+
+
+def test_batch_rows_are_independent():
+    w = Workload("bi", 3, 200, 2, state_out="bf16")
+    inp = make_inputs(w, seed=5)
+    out, hT = run_gpu(inp)
+    for b in range(3):
+        one = dict(inp)
+        for key in ("q", "k", "v", "g", "beta"):
+            one[key] = inp[key][b:b + 1].contiguous()
+        one["out"] = torch.zeros_like(one["v"])
+        one["final_state"] = torch.zeros_like(inp["final_state"][b:b + 1])
+        o1, h1 = run_gpu(one)
+        assert torch.equal(o1[0], out[b])
+        assert torch.equal(h1[0], hT[b])
+
+
+def test_out_rows_past_sequence_end_untouched_and_inputs_unmodified():
+    lens = [5, 20]
+    w = Workload("u", 1, 25, 2, seq_lens=lens)
+    inp = make_inputs(w, seed=6)
+    d = to_device(inp, "cuda")
+    keep = {key: d[key].clone() for key in ("q", "k", "v", "g", "beta")}
+    flashkda_b200.fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["out"], A_log=d["A_log"],
+                      dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], cu_seqlens=d["cu_seqlens"])
+    torch.cuda.synchronize()
+    for key, val in keep.items():
+        assert torch.equal(val, d[key])
+
+
+def test_host_argument_errors_on_gpu():
+    inp = to_device(make_inputs(Workload("e", 1, 32, 2)), "cuda")
+    args = lambda **kw: dict(dict(A_log=inp["A_log"], dt_bias=inp["dt_bias"], lower_bound=-5.0), **kw)
+    call = lambda **kw: flashkda_b200.fwd(kw.pop("q", inp["q"]), inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"],
+                                          inp["out"], **args(**kw))
+    with pytest.raises(RuntimeError, match="q must be bfloat16"):
+        call(q=inp["q"].float())
+    with pytest.raises(RuntimeError, match="A_log must be float32"):
+        call(A_log=inp["A_log"].double())
+    with pytest.raises(RuntimeError, match="same dtype"):
+        call(initial_state=torch.zeros(1, 2, 128, 128, device="cuda"),
+             final_state=torch.zeros(1, 2, 128, 128, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match=r"\[N, H, D, D\]"):
+        call(final_state=torch.zeros(2, 2, 128, 128, device="cuda"))
+    with pytest.raises(RuntimeError, match="cu_seqlens must be int64"):
+        call(cu_seqlens=torch.tensor([0, 32], device="cuda", dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="contiguous"):
+        call(q=inp["q"].transpose(1, 2))
