@@ -35,7 +35,9 @@ def run_gpu(inp, algo=None):
 
 def check_against(out, hT, ref_out, ref_hT):
     assert torch.isfinite(out.float()).all()
-    assert oracle.max_abs(ref_out, out) <= OUT_MAX_ABS
+    # absolute bound for O(1) outputs; fixtures with the reference's arange-valued initial state reach
+    # |out| ~ 1e3, where the bound scales with the magnitude
+    assert oracle.max_abs(ref_out, out) <= OUT_MAX_ABS * max(1.0, ref_out.float().abs().max().item())
     assert oracle.err_ratio(ref_out, out) <= OUT_RATIO
     if ref_hT is not None:
         assert hT is not None and torch.isfinite(hT.float()).all()
