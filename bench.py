@@ -225,6 +225,8 @@ def run_ours(a):
     launches_per_step = flashkda_b200.last_launch_count()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
+    dev_status = flashkda_b200.device_status(workspace)
+    assert dev_status == 0, f"device status {dev_status}: a kernel gave up on a bounded wait"
     t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -233,7 +235,8 @@ def run_ours(a):
     value = world * w.tokens / (ms_step * 1e-3)
 
     # ---- dominant kernel alone (CUDA events on the launching stream) ----
-    kernel_name, kernel_ms = "fkda::recurrence_kernel", None
+    kernel_name = {"tc": "fkda::recurrence_tc_kernel"}.get(algo, "fkda::recurrence_kernel")
+    kernel_ms = None
     n_phase = 3
     barrier()
     p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

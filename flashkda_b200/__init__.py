@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["fwd", "get_workspace_size", "last_launch_count", "default_algo"]
+__all__ = ["fwd", "get_workspace_size", "last_launch_count", "default_algo", "device_status"]
 
 D = 128
 _ENV_ALGO = "FLASHKDA_B200_ALGO"
@@ -129,6 +129,14 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
     # `workspace` was allocated on (or handed over for) the current stream, so the caching allocator
     # reuses it in stream order once this reference is dropped
     return None
+
+
+def device_status(workspace: torch.Tensor) -> int:
+    """Synchronises the current stream and returns the device status word of the last call that used
+    ``workspace`` (0 = ok; see ``fkda_device_status``)."""
+    with torch.cuda.device(workspace.device):
+        stream = torch.cuda.current_stream(workspace.device).cuda_stream
+        return int(_lib.lib().fkda_device_status(workspace.data_ptr(), stream))
 
 
 def last_launch_count() -> int:

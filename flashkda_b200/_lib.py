@@ -6,9 +6,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libflashkda_b200.so")
 
 FKDA_STATE_BF16, FKDA_STATE_FP32 = 0, 1
-ALGO_AUTO, ALGO_TWOPASS = 0, 1
+ALGO_AUTO, ALGO_TWOPASS, ALGO_TC = 0, 1, 2
 PHASE_PREPARE, PHASE_RECURRENCE = 1, 2
-ALGOS = {"auto": ALGO_AUTO, "twopass": ALGO_TWOPASS}
+ALGOS = {"auto": ALGO_AUTO, "twopass": ALGO_TWOPASS, "tc": ALGO_TC}
 
 
 class FwdParams(ctypes.Structure):
@@ -45,6 +45,8 @@ def lib():
         L.fkda_status_string.restype = ctypes.c_char_p
         L.fkda_status_string.argtypes = [ctypes.c_int]
         L.fkda_last_launch_count.restype = ctypes.c_int
+        L.fkda_device_status.restype = ctypes.c_int
+        L.fkda_device_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         _lib = L
     return _lib
 

@@ -37,11 +37,22 @@ size_t fkda_workspace_bytes(int64_t T_total, int64_t H, int64_t N, int32_t algo)
     if (T_total < 0 || H <= 0 || N < 0) return 0;
     switch (resolve_algo(algo)) {
         case FKDA_ALGO_TWOPASS: return fkda::twopass_workspace_bytes(T_total, H, N);
+        case FKDA_ALGO_TC: return fkda::tc_workspace_bytes(T_total, H, N);
         default: return 0;
     }
 }
 
 int fkda_last_launch_count(void) { return g_last_launches; }
+
+int fkda_device_status(const void* workspace, void* stream_v) {
+    if (workspace == nullptr) return FKDA_ERR_NULL_POINTER;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+    int32_t hdr[2] = {0, 0};
+    if (cudaMemcpyAsync(hdr, workspace, sizeof(hdr), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess)
+        return FKDA_ERR_LAUNCH;
+    return hdr[1] == 0 ? FKDA_OK : FKDA_ERR_DEVICE_STATUS;
+}
 
 int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
     g_last_launches = 0;
@@ -59,14 +70,15 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
         !aligned16(p->final_state))
         return FKDA_ERR_ALIGNMENT;
     const int algo = resolve_algo(p->algo);
-    if (algo != FKDA_ALGO_TWOPASS) return FKDA_ERR_BAD_ALGO;
+    if (algo != FKDA_ALGO_TWOPASS && algo != FKDA_ALGO_TC) return FKDA_ERR_BAD_ALGO;
     const size_t need = fkda_workspace_bytes(T_total, p->H, p->N, algo);
     if (need > 0 && (p->workspace == nullptr || p->workspace_bytes < need ||
                      (reinterpret_cast<uintptr_t>(p->workspace) & 255u) != 0))
         return FKDA_ERR_WORKSPACE;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     int launches = 0;
-    int rc = fkda::launch_twopass(*p, stream, &launches);
+    int rc = (algo == FKDA_ALGO_TC) ? fkda::launch_tc(*p, stream, &launches)
+                                    : fkda::launch_twopass(*p, stream, &launches);
     if (rc == FKDA_OK) g_last_launches = launches;
     return rc;
 }

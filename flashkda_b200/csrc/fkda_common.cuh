@@ -27,6 +27,26 @@ constexpr int kWsMqk = kWsInv + kChunk * kChunk * 2;
 constexpr int kWsRecord = kWsMqk + kChunk * kChunk * 2;  // 13824
 static_assert(kWsRecord == 13824, "workspace record size");
 
+// Record of the tensor-core two-pass workspace: operand tiles in the no-swizzle UMMA canonical
+// layouts (8 x 16-byte "core matrices" of 128 contiguous bytes):
+//   B1  [kd; qd] as the K-major B operand [32 rows, K=128]: byte = (k/8)*512 + (r/8)*128 + (r%8)*16 + (k%8)*2
+//   KR  kr as the MN-major B operand [N=128, K=16 tokens]:  byte = (i/8)*2048 + (n/8)*128 + (i%8)*16 + (n%8)*2
+//   INV, MQK as K-major B operands [16, 16]:                byte = (j/8)*256 + (i/8)*128 + (i%8)*16 + (j%8)*2
+//   ET  E_tot [128] f32;  BETA bf16-rounded sigmoid(beta) [16] widened to f32
+constexpr int kTcB1 = 0;
+constexpr int kTcKr = 8192;
+constexpr int kTcInv = 12288;
+constexpr int kTcMqk = 12800;
+constexpr int kTcEt = 13312;
+constexpr int kTcBeta = 13824;
+constexpr int kTcRecord = 13888;
+static_assert(kTcRecord % 16 == 0, "bulk copies move multiples of 16 bytes");
+__host__ __device__ constexpr int tc_b1_off(int r, int kc) { return kc * 512 + (r >> 3) * 128 + (r & 7) * 16; }
+__host__ __device__ constexpr int tc_kr_off(int i, int nc) { return (i >> 3) * 2048 + nc * 128 + (i & 7) * 16; }
+__host__ __device__ constexpr int tc_sq_off(int i, int j) {
+    return (j >> 3) * 256 + (i >> 3) * 128 + (i & 7) * 16 + (j & 7) * 2;
+}
+
 // ---- approximate transcendentals: the instructions are part of the contract ----
 __device__ __forceinline__ float ex2_approx(float x) {
     float r;
@@ -138,10 +158,11 @@ __device__ __forceinline__ Frag16 mma16x16_h(const Frag16& a, const Frag16& b) {
 //   (I + L)^-1 = (I - L)(I + L^2)(I + L^4)(I + L^8)
 // with fp16 products/accumulators and fp16 additions, result rounded to bf16
 // (csrc/smxx/utils.cuh:262-311; tests/torch_ref.py:221-229).
-// Ls: L (row-major, pitch ld); Ws: scratch 16 x ld halves; inv_out: bf16 [16][16] dense.
-// Both Ls and Ws are clobbered.  All 32 lanes of the warp must call.
-__device__ __forceinline__ void neumann_inverse_warp(__half* Ls, __half* Ws, int ld, __nv_bfloat16* inv_out,
-                                                     int lane) {
+// Ls: L (row-major, pitch ld); Ws: scratch 16 x ld halves; inv_out: bf16 [16][16], dense row-major
+// (kCanonical = false) or in the UMMA canonical K-major layout (tc_sq_off).  Ws is clobbered.
+// All 32 lanes of the warp must call.
+template <bool kCanonical>
+__device__ __forceinline__ void neumann_inverse_warp(__half* Ls, __half* Ws, int ld, uint8_t* inv_out, int lane) {
     const int g = lane >> 2, t = lane & 3;
     // INV0 = I - L in C-fragment coordinates
     Frag16 inv_c;
@@ -179,7 +200,8 @@ __device__ __forceinline__ void neumann_inverse_warp(__half* Ls, __half* Ws, int
     auto st = [&](int r, int c, uint32_t packed) {
         __half2 h = *reinterpret_cast<__half2*>(&packed);
         float2 f = __half22float2(h);
-        *reinterpret_cast<uint32_t*>(inv_out + r * kChunk + c) = pack_bf2(f.x, f.y);
+        const int off = kCanonical ? tc_sq_off(r, c) : (r * kChunk + c) * 2;
+        *reinterpret_cast<uint32_t*>(inv_out + off) = pack_bf2(f.x, f.y);
     };
     st(g, 2 * t, inv_c.r[0]);
     st(g + 8, 2 * t, inv_c.r[1]);

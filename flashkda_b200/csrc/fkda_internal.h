@@ -19,14 +19,31 @@ struct TwoPassArgs {
     void* final_state;
     const int64_t* cu_seqlens;
     int32_t* tile_prefix;  // [N + 1] chunk-count prefix (varlen only)
-    uint8_t* workspace;    // [H][total_tiles] records of kWsRecord bytes
+    uint8_t* workspace;    // [H][total_tiles] per-chunk records
+    int32_t* queue;        // work-queue counter of the persistent recurrence (zeroed per call)
+    int32_t* status;       // device status word: 0 ok, else the code of a bounded wait that gave up
     int64_t T, H, N, total_tiles;
     int64_t token_stride, beta_token_stride;
     float scale, gate_scale;
     bool state_fp32;
 };
 
+// Workspace layout of both two-pass implementations:
+//   [0, 256)  header: int32 queue counter, int32 device status
+//   [256, ..) tile prefix (N + 1 int32, padded to 256 B)
+//   then      H * total_tiles records
+constexpr size_t kWsHeaderBytes = 256;
+inline size_t ws_prefix_bytes(int64_t N) { return (size_t)(((N + 1) * 4 + 255) / 256 * 256); }
+inline int64_t ws_tiles_upper_bound(int64_t T_total, int64_t N) { return (T_total + 15) / 16 + N; }
+
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
 int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
+size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
+int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
+
+// Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
+// workspace carving).
+void fill_args(const fkda_fwd_params& p, TwoPassArgs* a);
+void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, cudaStream_t stream);
 
 }  // namespace fkda

@@ -1,0 +1,390 @@
+// Tensor-core two-pass KDA forward for sm_100a: the token-parallel prepare kernel writes per-chunk
+// operand records already laid out as tcgen05 (UMMA) shared-memory operands; a persistent
+// recurrence kernel walks the chunks of each (sequence, head) chain with
+//   * one bulk asynchronous copy (TMA engine) per chunk record + one per value row, double buffered,
+//   * the [128,128] bf16 state resident in shared memory as the A operand of the state contraction,
+//   * all contractions on tcgen05.mma with fp32 accumulators in tensor memory, in the transposed
+//     formulation that makes V = 128 the MMA M dimension:
+//        D1[V,32]  = S[V,K] . [kd; qd]^T          (8 x M128 N32 K16)
+//        D2[V,16]  = u'^T[V,16] . INV^T           (M128 N16 K16)
+//        D3[V,16]  = U^T[V,16] . Mqk^T            (M128 N16 K16)
+//        DS[V,K]   = U^T[V,16] . kr[16,K]         (M128 N128 K16, MN-major B)
+//   * element-wise steps (bf16 roundings, beta, gate decay) by 128 threads, one per V row, reading the
+//     accumulators with tcgen05.ld.
+// Three independent chains run per CTA (one warpgroup each) so that the tensor-core / barrier latency
+// of one chain is covered by the element-wise work of the others.
+//
+// Numerics: steps B1-B7 of the reference's contract (tests/torch_ref.py:231-251; the reference's own
+// recurrence is csrc/smxx/fwd_kernel2.cuh:434-742, built on mma.sync with register transposes).
+#include "fkda_common.cuh"
+#include "fkda_internal.h"
+#include "fkda_prepare.cuh"
+#include "fkda_sm100.cuh"
+
+namespace fkda {
+
+using namespace sm100;
+
+constexpr int kTcChains = 3;    // chains (warpgroups) per CTA
+constexpr int kTcStages = 2;    // chunk records in flight per chain
+constexpr int kTcTmemCols = 512;
+constexpr uint32_t kTcWaitNs = 2000000000u;
+
+// byte offsets inside one chain's shared-memory block
+constexpr int kSmS = 0;                                    // state, canonical K-major A operand [128, 128]
+constexpr int kSmStage = 32768;                            // kTcStages x (record + value tile)
+constexpr int kSmStageBytes = kTcRecord + kChunk * kD * 2; // 17984
+constexpr int kSmA23 = kSmStage + kTcStages * kSmStageBytes;  // A operand of the 16-deep products [128, 16]
+constexpr int kSmOut = kSmA23 + 4096;                      // out tile [16][128] bf16
+constexpr int kSmChainBytes = kSmOut + 4096;               // 76928
+static_assert(kSmChainBytes % 128 == 0, "chain blocks stay 128-byte aligned");
+
+struct TcCtrl {
+    uint64_t full[kTcChains][kTcStages];
+    uint64_t mma[kTcChains];
+    uint32_t tmem_base;
+    int32_t next_chain[kTcChains];
+    int32_t abort_flag;
+};
+constexpr int kTcSmemBytes = kTcChains * kSmChainBytes + (int)sizeof(TcCtrl) + 128;
+static_assert(kTcSmemBytes <= 232448, "exceeds the 227 KB shared-memory limit of a CTA");
+
+// state element (v, k..k+7) lives at kc*2048 + (v/8)*128 + (v%8)*16   (kc = k/8)
+__device__ __forceinline__ int s_off(int v, int kc) { return kc * 2048 + (v >> 3) * 128 + (v & 7) * 16; }
+
+__global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPassArgs a) {
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
+    TcCtrl& ctl = *reinterpret_cast<TcCtrl*>(smem + kTcChains * kSmChainBytes);
+
+    const int wg = threadIdx.x >> 7;   // chain slot
+    const int v = threadIdx.x & 127;   // state row = TMEM lane
+    const int warp = threadIdx.x >> 5;
+    uint8_t* cs = smem + wg * kSmChainBytes;
+    volatile int* abort_flag = &ctl.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int c = 0; c < kTcChains; ++c) {
+            for (int s = 0; s < kTcStages; ++s) mbar_init(&ctl.full[c][s], 1);
+            mbar_init(&ctl.mma[c], 1);
+        }
+        ctl.abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        __syncwarp();
+        tmem_alloc(&ctl.tmem_base, kTcTmemCols);
+        tmem_relinquish_alloc_permit();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctl.tmem_base;
+    // columns: DS of chain c at 128*c (128 wide), D1 of chain c at 384 + 32*c (32 wide; D2 reuses
+    // its first 16 columns and D3 its last 16 once D1 has been read)
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_ds = tmem_base + 128u * wg;
+    const uint32_t t_d1 = tmem_base + 384u + 32u * wg;
+
+    constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, false, false);
+    constexpr uint32_t idesc_n16 = make_idesc_bf16_f32(128, 16, false, false);
+    constexpr uint32_t idesc_ds = make_idesc_bf16_f32(128, 128, false, true);
+
+    const uint32_t s_addr = smem_u32(cs + kSmS);
+    const uint32_t a23_addr = smem_u32(cs + kSmA23);
+    const int bar_id = 1 + wg;
+    const int64_t n_chains = a.N * a.H;
+    uint32_t full_phase[kTcStages] = {0, 0};
+    uint32_t mma_phase = 0;
+    bool failed = false;
+
+    while (!failed) {
+        // ---- next chain from the work queue ----
+        if (v == 0) ctl.next_chain[wg] = atomicAdd(a.queue, 1);
+        named_barrier_sync(bar_id, 128);
+        const int64_t chain = ctl.next_chain[wg];
+        if (chain >= n_chains) break;
+        const int64_t n = chain / a.H;
+        const int h = (int)(chain - n * a.H);
+        int64_t bos, seq_len, tile_base;
+        if (a.cu_seqlens != nullptr) {
+            bos = a.cu_seqlens[n];
+            seq_len = a.cu_seqlens[n + 1] - bos;
+            if (seq_len < 0) seq_len = 0;
+            tile_base = a.tile_prefix[n];
+        } else {
+            bos = n * a.T;
+            seq_len = a.T;
+            tile_base = n * ((a.T + kChunk - 1) / kChunk);
+        }
+        const int64_t n_chunks = (seq_len + kChunk - 1) / kChunk;
+        const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
+        const int64_t st_off = (n * a.H + h) * (int64_t)(kD * kD) + (int64_t)v * kD;
+
+        auto issue_load = [&](int64_t t) {  // one thread: record + value rows of chunk t into stage t % 2
+            const int s = (int)(t % kTcStages);
+            const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
+            uint8_t* dst = cs + kSmStage + s * kSmStageBytes;
+            mbar_arrive_expect_tx(&ctl.full[wg][s], (uint32_t)(kTcRecord + len * kD * 2));
+            bulk_g2s(dst, rec_base + t * (int64_t)kTcRecord, kTcRecord, &ctl.full[wg][s]);
+            const __nv_bfloat16* vsrc = a.v + (bos + t * kChunk) * a.token_stride + (int64_t)h * kD;
+            for (int i = 0; i < len; ++i)
+                bulk_g2s(dst + kTcRecord + i * kD * 2, vsrc + i * a.token_stride, kD * 2, &ctl.full[wg][s]);
+        };
+        if (v == 0) {
+            for (int64_t t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
+        }
+
+        // ---- initial state into the canonical A-operand layout (fp32 rounded to bf16) ----
+        if (a.initial_state != nullptr) {
+            if (a.state_fp32) {
+                const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.initial_state) + st_off);
+#pragma unroll 4
+                for (int kc = 0; kc < 16; ++kc) {
+                    const float4 x = src[2 * kc], y = src[2 * kc + 1];
+                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc)) =
+                        make_uint4(pack_bf2(x.x, x.y), pack_bf2(x.z, x.w), pack_bf2(y.x, y.y), pack_bf2(y.z, y.w));
+                }
+            } else {
+                const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.initial_state) + st_off);
+#pragma unroll 4
+                for (int kc = 0; kc < 16; ++kc) *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc)) = src[kc];
+            }
+        } else {
+#pragma unroll 4
+            for (int kc = 0; kc < 16; ++kc) *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc)) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(bar_id, 128);
+
+        for (int64_t t = 0; t < n_chunks; ++t) {
+            const int s = (int)(t % kTcStages);
+            const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
+            uint8_t* st = cs + kSmStage + s * kSmStageBytes;
+            const uint32_t st_addr = smem_u32(st);
+
+            // ---- operands of chunk t have landed ----
+            if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
+            full_phase[s] ^= 1u;
+
+            // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
+            if (v == 0) {
+                tc_fence_after_sync();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint64_t ad = make_smem_desc(s_addr + j * 4096, 2048, 128);
+                    const uint64_t bd = make_smem_desc(st_addr + kTcB1 + j * 1024, 512, 128);
+                    umma_ss(t_d1, ad, bd, idesc_n32, j > 0 ? 1u : 0u);
+                }
+                umma_commit(&ctl.mma[wg]);
+            }
+            // value column of this thread, beta
+            float vv[kChunk];
+            {
+                const __nv_bfloat16* vt = reinterpret_cast<const __nv_bfloat16*>(st + kTcRecord);
+#pragma unroll
+                for (int i = 0; i < kChunk; ++i) vv[i] = (i < len) ? bf2f(vt[i * kD + v]) : 0.0f;
+            }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            mma_phase ^= 1u;
+            tc_fence_after_sync();
+
+            // ---- u' = (v - bf(u0)) * bf(beta) -> A operand; keep bf(o0) ----
+            uint32_t ob[8];
+            {
+                uint32_t r[32];
+                tmem_ld32(t_d1 + lane_sel, r);
+                tmem_wait_ld();
+                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
+                float up[kChunk];
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 b = bp[i4];
+                    const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = i4 * 4 + e;
+                        const float u0 = bf2f(f2bf(__uint_as_float(r[i])));
+                        const float d = bf2f(f2bf(__fsub_rn(vv[i], u0)));
+                        up[i] = __fmul_rn(d, bb[e]);  // rounded to bf16 by the pack below
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    ob[i] = pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1]));
+                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
+                *reinterpret_cast<uint4*>(ap) =
+                    make_uint4(pack_bf2(up[0], up[1]), pack_bf2(up[2], up[3]), pack_bf2(up[4], up[5]), pack_bf2(up[6], up[7]));
+                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(pack_bf2(up[8], up[9]), pack_bf2(up[10], up[11]),
+                                                                  pack_bf2(up[12], up[13]), pack_bf2(up[14], up[15]));
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            named_barrier_sync(bar_id, 128);
+
+            // ---- MMA2: D2[V,16] = u'^T . INV^T ----
+            if (v == 0) {
+                tc_fence_after_sync();
+                umma_ss(t_d1, make_smem_desc(a23_addr, 2048, 128), make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
+                umma_commit(&ctl.mma[wg]);
+            }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            mma_phase ^= 1u;
+            tc_fence_after_sync();
+            {
+                uint32_t r[16];
+                tmem_ld16(t_d1 + lane_sel, r);
+                tmem_wait_ld();
+                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
+                uint32_t p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
+                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            named_barrier_sync(bar_id, 128);
+
+            // ---- MMA3: D3[V,16] = U^T . Mqk^T ;  DS[V,K] = U^T . kr ----
+            if (v == 0) {
+                bulk_wait_group_read<0>();  // the previous out tile has been read by its bulk stores
+                tc_fence_after_sync();
+                const uint64_t ad = make_smem_desc(a23_addr, 2048, 128);
+                umma_ss(t_d1 + 16, ad, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
+                umma_ss(t_ds, ad, make_smem_desc(st_addr + kTcKr, 2048, 128), idesc_ds, 0u);
+                umma_commit(&ctl.mma[wg]);
+            }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            mma_phase ^= 1u;
+            tc_fence_after_sync();
+
+            // ---- out = bf(o0) (+) bf(Mqk U) into the out tile ----
+            {
+                uint32_t r[16];
+                tmem_ld16(t_d1 + 16 + lane_sel, r);
+                tmem_wait_ld();
+                __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(cs + kSmOut);
+#pragma unroll
+                for (int i = 0; i < kChunk; ++i) {
+                    const float o0 = (i & 1) ? bf_hi(ob[i >> 1]) : bf_lo(ob[i >> 1]);
+                    ot[i * kD + v] = f2bf(__fadd_rn(o0, bf2f(f2bf(__uint_as_float(r[i])))));
+                }
+            }
+            // ---- S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])) ----
+#pragma unroll 1
+            for (int cb = 0; cb < 4; ++cb) {
+                uint32_t r[32];
+                tmem_ld32(t_ds + cb * 32 + lane_sel, r);
+                tmem_wait_ld();
+                const float4* ep = reinterpret_cast<const float4*>(st + kTcEt) + cb * 8;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int kc = cb * 4 + q4;
+                    uint4* sp = reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc));
+                    const uint4 sv = *sp;
+                    const float4 e0 = ep[2 * q4], e1 = ep[2 * q4 + 1];
+                    const uint32_t* rr = r + q4 * 8;
+                    uint4 nv;
+                    nv.x = pack_bf2(__fmaf_rn(bf_lo(sv.x), e0.x, __uint_as_float(rr[0])),
+                                    __fmaf_rn(bf_hi(sv.x), e0.y, __uint_as_float(rr[1])));
+                    nv.y = pack_bf2(__fmaf_rn(bf_lo(sv.y), e0.z, __uint_as_float(rr[2])),
+                                    __fmaf_rn(bf_hi(sv.y), e0.w, __uint_as_float(rr[3])));
+                    nv.z = pack_bf2(__fmaf_rn(bf_lo(sv.z), e1.x, __uint_as_float(rr[4])),
+                                    __fmaf_rn(bf_hi(sv.z), e1.y, __uint_as_float(rr[5])));
+                    nv.w = pack_bf2(__fmaf_rn(bf_lo(sv.w), e1.z, __uint_as_float(rr[6])),
+                                    __fmaf_rn(bf_hi(sv.w), e1.w, __uint_as_float(rr[7])));
+                    *sp = nv;
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            named_barrier_sync(bar_id, 128);
+
+            // ---- store the out rows, refill the stage ----
+            if (v == 0) {
+                __nv_bfloat16* dst = a.out + (bos + t * kChunk) * a.token_stride + (int64_t)h * kD;
+                for (int i = 0; i < len; ++i) bulk_s2g(dst + i * a.token_stride, cs + kSmOut + i * kD * 2, kD * 2);
+                bulk_commit_group();
+                if (t + kTcStages < n_chunks) issue_load(t + kTcStages);
+            }
+        }
+        if (failed) break;
+
+        // ---- final state: bf16, or the bf16 state widened to fp32 ----
+        if (a.final_state != nullptr) {
+            if (a.state_fp32) {
+                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.final_state) + st_off);
+#pragma unroll 4
+                for (int kc = 0; kc < 16; ++kc) {
+                    const uint4 sv = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, kc));
+                    dst[2 * kc] = make_float4(bf_lo(sv.x), bf_hi(sv.x), bf_lo(sv.y), bf_hi(sv.y));
+                    dst[2 * kc + 1] = make_float4(bf_lo(sv.z), bf_hi(sv.z), bf_lo(sv.w), bf_hi(sv.w));
+                }
+            } else {
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.final_state) + st_off);
+#pragma unroll 4
+                for (int kc = 0; kc < 16; ++kc) dst[kc] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, kc));
+            }
+        }
+        // all rows exported and all operand reads done before the next chain overwrites S / the stages
+        named_barrier_sync(bar_id, 128);
+    }
+
+    if (failed) {
+        ctl.abort_flag = 1;
+        atomicExch(a.status, FKDA_ERR_DEVICE_STATUS);
+    }
+    if (v == 0) bulk_wait_group<0>();  // this thread's out stores have fully completed
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTcTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
+    return kWsHeaderBytes + ws_prefix_bytes(N) +
+           (size_t)H * (size_t)ws_tiles_upper_bound(T_total, N) * (size_t)kTcRecord;
+}
+
+int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
+    TwoPassArgs a;
+    fill_args(p, &a);
+    const bool varlen = p.cu_seqlens != nullptr;
+    const bool do_prep = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_PREPARE);
+    const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
+    int launches = 0;
+    if (cudaMemsetAsync(p.workspace, 0, 8, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;  // queue + status
+    if (varlen && do_prep) {
+        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, stream);
+        ++launches;
+    }
+    if (a.total_tiles > 0 && do_prep) {
+        dim3 grid1((unsigned)a.total_tiles, (unsigned)p.H);
+        prepare_kernel<true><<<grid1, 256, 0, stream>>>(a);
+        ++launches;
+    }
+    if (do_rec) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return FKDA_ERR_LAUNCH;
+        if (cudaFuncSetAttribute(recurrence_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
+            cudaSuccess)
+            return FKDA_ERR_LAUNCH;
+        const int64_t chains = p.N * p.H;
+        int64_t ctas = (chains + kTcChains - 1) / kTcChains;
+        if (ctas > sms) ctas = sms;
+        if (ctas < 1) ctas = 1;
+        recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a);
+        ++launches;
+    }
+    if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
+    *n_launches = launches;
+    return FKDA_OK;
+}
+
+}  // namespace fkda

@@ -45,7 +45,8 @@ enum { FKDA_PHASE_PREPARE = 1, FKDA_PHASE_RECURRENCE = 2 };
 /* Which device implementation runs. */
 enum {
     FKDA_ALGO_AUTO = 0,
-    FKDA_ALGO_TWOPASS = 1 /* prepare kernel -> HBM workspace -> recurrence kernel (CUDA cores) */
+    FKDA_ALGO_TWOPASS = 1, /* prepare kernel -> HBM workspace -> recurrence kernel (CUDA cores) */
+    FKDA_ALGO_TC = 2       /* prepare kernel -> HBM workspace -> persistent tcgen05/TMEM recurrence */
 };
 
 /*
@@ -90,6 +91,11 @@ size_t fkda_workspace_bytes(int64_t T_total, int64_t H, int64_t N, int32_t algo)
 
 /* Enqueues the forward pass on `stream` (a cudaStream_t passed as void*). */
 int fkda_fwd(const fkda_fwd_params* p, void* stream);
+
+/* Synchronises `stream`, then reads the device status word that the kernels of the last call
+ * using `workspace` left there: FKDA_OK, or FKDA_ERR_DEVICE_STATUS when a kernel gave up on one of
+ * its bounded internal waits (its outputs are then invalid).  Other failures: FKDA_ERR_LAUNCH. */
+int fkda_device_status(const void* workspace, void* stream);
 
 /* Library ABI version (major * 1000 + minor). */
 int fkda_version(void);
