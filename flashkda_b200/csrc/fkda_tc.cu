@@ -25,6 +25,14 @@ namespace fkda {
 
 using namespace sm100;
 
+// Profiling aid (off by default): with -DFKDA_TC_TIMING thread 0 of CTA 0 stores clock64() deltas of
+// the stages of its 64th chunk into the workspace header (ints 16..31).
+#ifdef FKDA_TC_TIMING
+#define TC_STAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && t == 64) stamps[i] = clock64(); } while (0)
+#else
+#define TC_STAMP(i) do { } while (0)
+#endif
+
 constexpr int kTcChains = 3;    // chains (warpgroups) per CTA
 constexpr int kTcStages = 2;    // chunk records in flight per chain
 constexpr int kTcTmemCols = 512;
@@ -97,6 +105,9 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
     uint32_t full_phase[kTcStages] = {0, 0};
     uint32_t mma_phase = 0;
     bool failed = false;
+#ifdef FKDA_TC_TIMING
+    long long stamps[16] = {0};
+#endif
 
     while (!failed) {
         // ---- next chain from the work queue ----
@@ -166,6 +177,10 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             // ---- operands of chunk t have landed ----
             if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
             full_phase[s] ^= 1u;
+            TC_STAMP(0);
+#ifdef FKDA_TC_TIMING
+            if (blockIdx.x == 0 && threadIdx.x == 0 && t == 65) stamps[12] = clock64();
+#endif
 
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
             if (v == 0) {
@@ -178,6 +193,7 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
                 }
                 umma_commit(&ctl.mma[wg]);
             }
+            TC_STAMP(1);
             // value column of this thread, beta
             float vv[kChunk];
             {
@@ -188,6 +204,7 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
+            TC_STAMP(2);
 
             // ---- u' = (v - bf(u0)) * bf(beta) -> A operand; keep bf(o0) ----
             uint32_t ob[8];
@@ -218,9 +235,11 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
                 *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(pack_bf2(up[8], up[9]), pack_bf2(up[10], up[11]),
                                                                   pack_bf2(up[12], up[13]), pack_bf2(up[14], up[15]));
             }
+            TC_STAMP(3);
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
+            TC_STAMP(4);
 
             // ---- MMA2: D2[V,16] = u'^T . INV^T ----
             if (v == 0) {
@@ -231,6 +250,7 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
+            TC_STAMP(5);
             {
                 uint32_t r[16];
                 tmem_ld16(t_d1 + lane_sel, r);
@@ -245,6 +265,7 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
+            TC_STAMP(6);
 
             // ---- MMA3: D3[V,16] = U^T . Mqk^T ;  DS[V,K] = U^T . kr ----
             if (v == 0) {
@@ -258,6 +279,7 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
+            TC_STAMP(7);
 
             // ---- out = bf(o0) (+) bf(Mqk U) into the out tile ----
             {
@@ -271,6 +293,7 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
                     ot[i * kD + v] = f2bf(__fadd_rn(o0, bf2f(f2bf(__uint_as_float(r[i])))));
                 }
             }
+            TC_STAMP(8);
             // ---- S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])) ----
 #pragma unroll 1
             for (int cb = 0; cb < 4; ++cb) {
@@ -297,9 +320,11 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
                     *sp = nv;
                 }
             }
+            TC_STAMP(9);
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
+            TC_STAMP(10);
 
             // ---- store the out rows, refill the stage ----
             if (v == 0) {
@@ -308,6 +333,12 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
                 bulk_commit_group();
                 if (t + kTcStages < n_chunks) issue_load(t + kTcStages);
             }
+            TC_STAMP(11);
+#ifdef FKDA_TC_TIMING
+            if (blockIdx.x == 0 && threadIdx.x == 0 && t == 65) {
+                for (int i = 0; i < 13; ++i) a.status[15 + i] = (int)(stamps[i] - stamps[0]);
+            }
+#endif
         }
         if (failed) break;
 

@@ -77,6 +77,11 @@ def config(name: str) -> Workload:
         return Workload("cfg4", B=8, T=32768, H=64, lower_bound=-3.0, state_in="fp32", state_out="fp32")
     if name == "cfg5":   # one long sequence (context-parallel case)
         return Workload("cfg5", B=1, T=1048576, H=32, lower_bound=-5.0, state_out="fp32")
+    if "=" in name:      # ad-hoc shape, e.g. "B=1,T=4096,H=444,state=fp32,lb=-5"
+        kv = dict(item.split("=") for item in name.split(","))
+        st = kv.get("state")
+        return Workload(name, B=int(kv.get("B", 1)), T=int(kv["T"]), H=int(kv["H"]),
+                        lower_bound=float(kv.get("lb", -5.0)), state_in=st, state_out=st)
     raise KeyError(name)
 
 
