@@ -45,6 +45,9 @@ def lib():
         L.fkda_status_string.restype = ctypes.c_char_p
         L.fkda_status_string.argtypes = [ctypes.c_int]
         L.fkda_last_launch_count.restype = ctypes.c_int
+        L.fkda_fwd_noalloc.restype = ctypes.c_int
+        L.fkda_fwd_noalloc.argtypes = [ctypes.POINTER(FwdParams), ctypes.c_void_p]
+        L.fkda_noalloc_scratch_bytes.restype = ctypes.c_size_t
         L.fkda_device_status.restype = ctypes.c_int
         L.fkda_device_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         _lib = L

@@ -24,6 +24,8 @@ const char* fkda_status_string(int status) {
         case FKDA_ERR_LAUNCH: return "a kernel launch or CUDA runtime call failed";
         case FKDA_ERR_ALIGNMENT: return "tensor base addresses and token strides must be 16-byte aligned";
         case FKDA_ERR_DEVICE_STATUS: return "a kernel reported an internal time-out";
+        case FKDA_ERR_NOALLOC_TOO_LARGE:
+            return "problem too large for the built-in scratch of fkda_fwd_noalloc (use fkda_fwd with a workspace)";
         default: return "unknown status";
     }
 }

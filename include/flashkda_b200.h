@@ -35,7 +35,8 @@ enum {
     FKDA_ERR_BAD_ALGO = 6,
     FKDA_ERR_LAUNCH = 7,         /* a kernel launch or CUDA runtime call failed */
     FKDA_ERR_ALIGNMENT = 8,      /* a tensor base address or stride is not 16-byte aligned */
-    FKDA_ERR_DEVICE_STATUS = 9   /* a kernel gave up on a bounded internal wait */
+    FKDA_ERR_DEVICE_STATUS = 9,  /* a kernel gave up on a bounded internal wait */
+    FKDA_ERR_NOALLOC_TOO_LARGE = 10 /* problem needs more scratch than fkda_fwd_noalloc has built in */
 };
 
 enum { FKDA_STATE_BF16 = 0, FKDA_STATE_FP32 = 1 };
@@ -96,6 +97,33 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream);
  * using `workspace` left there: FKDA_OK, or FKDA_ERR_DEVICE_STATUS when a kernel gave up on one of
  * its bounded internal waits (its outputs are then invalid).  Other failures: FKDA_ERR_LAUNCH. */
 int fkda_device_status(const void* workspace, void* stream);
+
+/*
+ * fkda_fwd_noalloc: fkda_fwd for callers that cannot allocate device memory (no counterpart in the
+ * reference, whose wrapper allocates a workspace tensor on every call).
+ *
+ * Some callers cannot call cudaMalloc or a framework allocator at the point where they need the
+ * forward pass: a serving loop whose device memory is wholly owned by a pool, a plugin called from
+ * another library's callback, a latency-critical thread that must not take allocator locks.  They
+ * pass inputs and outputs as usual and leave `workspace` / `workspace_bytes` unset (both are
+ * ignored); the per-chunk scratch comes from a fixed array of FKDA_NOALLOC_SCRATCH_BYTES bytes that
+ * every GPU loading this library holds until the process exits.
+ *
+ * Limit: fkda_workspace_bytes(B*T, H, N, algo) must not exceed FKDA_NOALLOC_SCRATCH_BYTES
+ * (roughly H * (B*T/16 + N) <= 2400 chunk records); larger problems return
+ * FKDA_ERR_NOALLOC_TOO_LARGE and launch nothing.
+ * The call itself performs no cudaMalloc/cudaFree and calls no allocating library routine.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call outside of any stream capture.
+ * All calls on a device share the one array: calls whose kernels may overlap on the GPU race with
+ * each other, so serialise them (one stream, or explicit ordering).  The array is not cleared
+ * between calls; the header words that must start at zero are reset by each call.
+ */
+#define FKDA_NOALLOC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int fkda_fwd_noalloc(const fkda_fwd_params* p, void* stream);
+
+/* Size of the built-in scratch of fkda_fwd_noalloc, as compiled into the loaded library. */
+size_t fkda_noalloc_scratch_bytes(void);
 
 /* Library ABI version (major * 1000 + minor). */
 int fkda_version(void);
