@@ -84,6 +84,20 @@ __device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// packed bf16x2 arithmetic: one round-to-nearest-even per element, as the scalar helpers above
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_add(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
 // ---- warp-level mma.sync m16n8k16, fp16 operands AND fp16 accumulators ----
 // (the instruction the reference's inverse uses: csrc/smxx/utils.cuh:199-260)
 __device__ __forceinline__ void mma_f16_f16acc(uint32_t& d0, uint32_t& d1, uint32_t a0, uint32_t a1, uint32_t a2,

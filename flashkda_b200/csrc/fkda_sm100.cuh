@@ -61,6 +61,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return true;
 }
 
+// One lane of a fully converged warp is elected (the same one every time).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ------------------------------------------------------------ proxy fences ----
 // generic-proxy writes to shared memory -> visible to the async proxy (bulk copies, tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async_smem() {

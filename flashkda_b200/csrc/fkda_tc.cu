@@ -1,7 +1,8 @@
 // Tensor-core two-pass KDA forward for sm_100a: the token-parallel prepare kernel writes per-chunk
 // operand records already laid out as tcgen05 (UMMA) shared-memory operands; a persistent
 // recurrence kernel walks the chunks of each (sequence, head) chain with
-//   * one bulk asynchronous copy (TMA engine) per chunk record + one per value row, double buffered,
+//   * one bulk asynchronous copy (TMA engine) per chunk record, double buffered on mbarriers; value
+//     columns prefetched into registers one chunk ahead, out rows stored from registers,
 //   * the [128,128] bf16 state resident in shared memory as the A operand of the state contraction,
 //   * all contractions on tcgen05.mma with fp32 accumulators in tensor memory, in the transposed
 //     formulation that makes V = 128 the MMA M dimension:
@@ -41,10 +42,9 @@ constexpr uint32_t kTcWaitNs = 2000000000u;
 // byte offsets inside one chain's shared-memory block
 constexpr int kSmS = 0;                                    // state, canonical K-major A operand [128, 128]
 constexpr int kSmStage = 32768;                            // kTcStages x (record + value tile)
-constexpr int kSmStageBytes = kTcRecord + kChunk * kD * 2; // 17984
+constexpr int kSmStageBytes = kTcRecord;                   // 13888
 constexpr int kSmA23 = kSmStage + kTcStages * kSmStageBytes;  // A operand of the 16-deep products [128, 16]
-constexpr int kSmOut = kSmA23 + 4096;                      // out tile [16][128] bf16
-constexpr int kSmChainBytes = kSmOut + 4096;               // 76928
+constexpr int kSmChainBytes = kSmA23 + 4096;               // 64640
 static_assert(kSmChainBytes % 128 == 0, "chain blocks stay 128-byte aligned");
 
 struct TcCtrl {
@@ -65,9 +65,12 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
     TcCtrl& ctl = *reinterpret_cast<TcCtrl*>(smem + kTcChains * kSmChainBytes);
 
-    const int wg = threadIdx.x >> 7;   // chain slot
+    // warp-uniform role indices (the shuffle makes the uniformity visible to the compiler, so the
+    // single-thread tcgen05 issue below sits in warp-uniform control flow)
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int wg = warp >> 2;          // chain slot
+    const int wiw = warp & 3;          // warp within the warpgroup
     const int v = threadIdx.x & 127;   // state row = TMEM lane
-    const int warp = threadIdx.x >> 5;
     uint8_t* cs = smem + wg * kSmChainBytes;
     volatile int* abort_flag = &ctl.abort_flag;
 
@@ -100,13 +103,15 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
 
     const uint32_t s_addr = smem_u32(cs + kSmS);
     const uint32_t a23_addr = smem_u32(cs + kSmA23);
+    const uint64_t s_desc0 = make_smem_desc(s_addr, 2048, 128);      // + 256 per K step of 16 (4096 B >> 4)
+    const uint64_t a23_desc = make_smem_desc(a23_addr, 2048, 128);
     const int bar_id = 1 + wg;
     const int64_t n_chains = a.N * a.H;
     uint32_t full_phase[kTcStages] = {0, 0};
     uint32_t mma_phase = 0;
     bool failed = false;
 #ifdef FKDA_TC_TIMING
-    long long stamps[16] = {0};
+    long long stamps[24] = {0};
 #endif
 
     while (!failed) {
@@ -132,19 +137,31 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
         const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
         const int64_t st_off = (n * a.H + h) * (int64_t)(kD * kD) + (int64_t)v * kD;
 
-        auto issue_load = [&](int64_t t) {  // one thread: record + value rows of chunk t into stage t % 2
+        auto issue_load = [&](int64_t t) {  // one thread: the record of chunk t into stage t % kTcStages
             const int s = (int)(t % kTcStages);
-            const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
-            uint8_t* dst = cs + kSmStage + s * kSmStageBytes;
-            mbar_arrive_expect_tx(&ctl.full[wg][s], (uint32_t)(kTcRecord + len * kD * 2));
-            bulk_g2s(dst, rec_base + t * (int64_t)kTcRecord, kTcRecord, &ctl.full[wg][s]);
-            const __nv_bfloat16* vsrc = a.v + (bos + t * kChunk) * a.token_stride + (int64_t)h * kD;
-            for (int i = 0; i < len; ++i)
-                bulk_g2s(dst + kTcRecord + i * kD * 2, vsrc + i * a.token_stride, kD * 2, &ctl.full[wg][s]);
+            mbar_arrive_expect_tx(&ctl.full[wg][s], (uint32_t)kTcRecord);
+            bulk_g2s(cs + kSmStage + s * kSmStageBytes, rec_base + t * (int64_t)kTcRecord, kTcRecord,
+                     &ctl.full[wg][s]);
         };
         if (v == 0) {
             for (int64_t t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
         }
+        // value column of this thread for chunk t: rows (2i, 2i+1) packed as bf16x2, zero past the end;
+        // fetched straight from global memory one chunk ahead (64 contiguous bytes per warp and row)
+        const unsigned short* vcol = reinterpret_cast<const unsigned short*>(a.v) + bos * a.token_stride +
+                                     (int64_t)h * kD + v;
+        // (the raw 16-bit values are kept apart until they are used, so the loads stay in flight)
+        auto load_v = [&](int64_t t, unsigned short (&dst)[kChunk]) {
+            const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
+            const unsigned short* p = vcol + t * kChunk * a.token_stride;
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+                dst[i] = (i < len) ? __ldg(p) : (unsigned short)0;
+                p += a.token_stride;
+            }
+        };
+        unsigned short v_cur[kChunk], v_nxt[kChunk];
+        if (n_chunks > 0) load_v(0, v_cur);
 
         // ---- initial state into the canonical A-operand layout (fp32 rounded to bf16) ----
         if (a.initial_state != nullptr) {
@@ -168,12 +185,30 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
         fence_proxy_async_smem();
         named_barrier_sync(bar_id, 128);
 
+        // out rows of the previous chunk, finished while the next chunk's first MMA runs
+        uint32_t o_pend[8];
+        int64_t o_pend_t = -1;
+        auto flush_out = [&]() {
+            if (o_pend_t < 0) return;
+            const int len = (int)min((int64_t)kChunk, seq_len - o_pend_t * kChunk);
+            unsigned short* dst = reinterpret_cast<unsigned short*>(a.out) +
+                                  (bos + o_pend_t * kChunk) * a.token_stride + (int64_t)h * kD + v;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (2 * i < len) *dst = (unsigned short)(o_pend[i] & 0xffffu);
+                dst += a.token_stride;
+                if (2 * i + 1 < len) *dst = (unsigned short)(o_pend[i] >> 16);
+                dst += a.token_stride;
+            }
+            o_pend_t = -1;
+        };
+
         for (int64_t t = 0; t < n_chunks; ++t) {
             const int s = (int)(t % kTcStages);
-            const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
             uint8_t* st = cs + kSmStage + s * kSmStageBytes;
             const uint32_t st_addr = smem_u32(st);
 
+            TC_STAMP(8);
             // ---- operands of chunk t have landed ----
             if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
             full_phase[s] ^= 1u;
@@ -183,57 +218,53 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
 #endif
 
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
-            if (v == 0) {
-                tc_fence_after_sync();
+            if (wiw == 0) {
+                if (elect_one()) {
+                    tc_fence_after_sync();
+                    const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, 512, 128);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint64_t ad = make_smem_desc(s_addr + j * 4096, 2048, 128);
-                    const uint64_t bd = make_smem_desc(st_addr + kTcB1 + j * 1024, 512, 128);
-                    umma_ss(t_d1, ad, bd, idesc_n32, j > 0 ? 1u : 0u);
+                    for (int j = 0; j < 8; ++j)
+                        umma_ss(t_d1, s_desc0 + (uint64_t)(j * 256), bd0 + (uint64_t)(j * 64), idesc_n32, j > 0 ? 1u : 0u);
+                    umma_commit(&ctl.mma[wg]);
                 }
-                umma_commit(&ctl.mma[wg]);
+                __syncwarp();
             }
             TC_STAMP(1);
-            // value column of this thread, beta
-            float vv[kChunk];
-            {
-                const __nv_bfloat16* vt = reinterpret_cast<const __nv_bfloat16*>(st + kTcRecord);
+            // work off the critical path while the MMA runs
+            flush_out();
+            TC_STAMP(13);
+            if (t + 1 < n_chunks) load_v(t + 1, v_nxt);
+            TC_STAMP(14);
+            const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
+            uint32_t bpk[8];
 #pragma unroll
-                for (int i = 0; i < kChunk; ++i) vv[i] = (i < len) ? bf2f(vt[i * kD + v]) : 0.0f;
+            for (int i4 = 0; i4 < 4; ++i4) {
+                const float4 b = bp[i4];
+                bpk[2 * i4] = pack_bf2(b.x, b.y);  // exact: the record holds bf16-rounded values
+                bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
             }
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(2);
 
-            // ---- u' = (v - bf(u0)) * bf(beta) -> A operand; keep bf(o0) ----
+            // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand; keep bf(o0) ----
             uint32_t ob[8];
             {
                 uint32_t r[32];
                 tmem_ld32(t_d1 + lane_sel, r);
                 tmem_wait_ld();
-                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
-                float up[kChunk];
+                uint32_t up[8];
 #pragma unroll
-                for (int i4 = 0; i4 < 4; ++i4) {
-                    const float4 b = bp[i4];
-                    const float bb[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = i4 * 4 + e;
-                        const float u0 = bf2f(f2bf(__uint_as_float(r[i])));
-                        const float d = bf2f(f2bf(__fsub_rn(vv[i], u0)));
-                        up[i] = __fmul_rn(d, bb[e]);  // rounded to bf16 by the pack below
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
+                    up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
                     ob[i] = pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1]));
+                }
                 uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                *reinterpret_cast<uint4*>(ap) =
-                    make_uint4(pack_bf2(up[0], up[1]), pack_bf2(up[2], up[3]), pack_bf2(up[4], up[5]), pack_bf2(up[6], up[7]));
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(pack_bf2(up[8], up[9]), pack_bf2(up[10], up[11]),
-                                                                  pack_bf2(up[12], up[13]), pack_bf2(up[14], up[15]));
+                *reinterpret_cast<uint4*>(ap) = make_uint4(up[0], up[1], up[2], up[3]);
+                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(up[4], up[5], up[6], up[7]);
             }
             TC_STAMP(3);
             fence_proxy_async_smem();
@@ -242,10 +273,13 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             TC_STAMP(4);
 
             // ---- MMA2: D2[V,16] = u'^T . INV^T ----
-            if (v == 0) {
-                tc_fence_after_sync();
-                umma_ss(t_d1, make_smem_desc(a23_addr, 2048, 128), make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
-                umma_commit(&ctl.mma[wg]);
+            if (wiw == 0) {
+                if (elect_one()) {
+                    tc_fence_after_sync();
+                    umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
+                    umma_commit(&ctl.mma[wg]);
+                }
+                __syncwarp();
             }
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
@@ -268,57 +302,73 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             TC_STAMP(6);
 
             // ---- MMA3: D3[V,16] = U^T . Mqk^T ;  DS[V,K] = U^T . kr ----
-            if (v == 0) {
-                bulk_wait_group_read<0>();  // the previous out tile has been read by its bulk stores
-                tc_fence_after_sync();
-                const uint64_t ad = make_smem_desc(a23_addr, 2048, 128);
-                umma_ss(t_d1 + 16, ad, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
-                umma_ss(t_ds, ad, make_smem_desc(st_addr + kTcKr, 2048, 128), idesc_ds, 0u);
-                umma_commit(&ctl.mma[wg]);
+            if (wiw == 0) {
+                if (elect_one()) {
+                    tc_fence_after_sync();
+                    umma_ss(t_d1 + 16, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
+                    umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcKr, 2048, 128), idesc_ds, 0u);
+                    umma_commit(&ctl.mma[wg]);
+                }
+                __syncwarp();
             }
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(7);
 
-            // ---- out = bf(o0) (+) bf(Mqk U) into the out tile ----
-            {
-                uint32_t r[16];
-                tmem_ld16(t_d1 + 16 + lane_sel, r);
-                tmem_wait_ld();
-                __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(cs + kSmOut);
-#pragma unroll
-                for (int i = 0; i < kChunk; ++i) {
-                    const float o0 = (i & 1) ? bf_hi(ob[i >> 1]) : bf_lo(ob[i >> 1]);
-                    ot[i * kD + v] = f2bf(__fadd_rn(o0, bf2f(f2bf(__uint_as_float(r[i])))));
-                }
-            }
-            TC_STAMP(8);
-            // ---- S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])) ----
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                uint32_t r[32];
-                tmem_ld32(t_ds + cb * 32 + lane_sel, r);
-                tmem_wait_ld();
+            // ---- S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])), TMEM loads one batch ahead;
+            //      out = bf(o0) (+) bf(Mqk U) is only formed here, its stores wait for the next MMA1 ----
+            auto update_cols = [&](int cb, const uint32_t (&r)[32]) {
+                // all loads of the batch first: the stores below may alias them as far as the compiler knows
                 const float4* ep = reinterpret_cast<const float4*>(st + kTcEt) + cb * 8;
+                uint4 sv[4];
+                float4 e[8];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) sv[q4] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, cb * 4 + q4));
+#pragma unroll
+                for (int q = 0; q < 8; ++q) e[q] = ep[q];
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int kc = cb * 4 + q4;
-                    uint4* sp = reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc));
-                    const uint4 sv = *sp;
-                    const float4 e0 = ep[2 * q4], e1 = ep[2 * q4 + 1];
+                    const float4 e0 = e[2 * q4], e1 = e[2 * q4 + 1];
                     const uint32_t* rr = r + q4 * 8;
                     uint4 nv;
-                    nv.x = pack_bf2(__fmaf_rn(bf_lo(sv.x), e0.x, __uint_as_float(rr[0])),
-                                    __fmaf_rn(bf_hi(sv.x), e0.y, __uint_as_float(rr[1])));
-                    nv.y = pack_bf2(__fmaf_rn(bf_lo(sv.y), e0.z, __uint_as_float(rr[2])),
-                                    __fmaf_rn(bf_hi(sv.y), e0.w, __uint_as_float(rr[3])));
-                    nv.z = pack_bf2(__fmaf_rn(bf_lo(sv.z), e1.x, __uint_as_float(rr[4])),
-                                    __fmaf_rn(bf_hi(sv.z), e1.y, __uint_as_float(rr[5])));
-                    nv.w = pack_bf2(__fmaf_rn(bf_lo(sv.w), e1.z, __uint_as_float(rr[6])),
-                                    __fmaf_rn(bf_hi(sv.w), e1.w, __uint_as_float(rr[7])));
-                    *sp = nv;
+                    nv.x = pack_bf2(__fmaf_rn(bf_lo(sv[q4].x), e0.x, __uint_as_float(rr[0])),
+                                    __fmaf_rn(bf_hi(sv[q4].x), e0.y, __uint_as_float(rr[1])));
+                    nv.y = pack_bf2(__fmaf_rn(bf_lo(sv[q4].y), e0.z, __uint_as_float(rr[2])),
+                                    __fmaf_rn(bf_hi(sv[q4].y), e0.w, __uint_as_float(rr[3])));
+                    nv.z = pack_bf2(__fmaf_rn(bf_lo(sv[q4].z), e1.x, __uint_as_float(rr[4])),
+                                    __fmaf_rn(bf_hi(sv[q4].z), e1.y, __uint_as_float(rr[5])));
+                    nv.w = pack_bf2(__fmaf_rn(bf_lo(sv[q4].w), e1.z, __uint_as_float(rr[6])),
+                                    __fmaf_rn(bf_hi(sv[q4].w), e1.w, __uint_as_float(rr[7])));
+                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, cb * 4 + q4)) = nv;
                 }
+            };
+            {
+                uint32_t r3[16], ra[32], rb[32];
+                tmem_ld32(t_ds + lane_sel, ra);
+                tmem_ld16(t_d1 + 16 + lane_sel, r3);
+                TC_STAMP(16);
+                tmem_wait_ld();
+                TC_STAMP(17);
+                tmem_ld32(t_ds + 32 + lane_sel, rb);
+                TC_STAMP(18);
+                update_cols(0, ra);
+                TC_STAMP(19);
+                tmem_wait_ld();
+                TC_STAMP(20);
+                tmem_ld32(t_ds + 64 + lane_sel, ra);
+                update_cols(1, rb);
+                TC_STAMP(21);
+                tmem_wait_ld();
+                TC_STAMP(22);
+                tmem_ld32(t_ds + 96 + lane_sel, rb);
+                update_cols(2, ra);
+                tmem_wait_ld();
+                update_cols(3, rb);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    o_pend[i] = bf2_add(ob[i], pack_bf2(__uint_as_float(r3[2 * i]), __uint_as_float(r3[2 * i + 1])));
+                o_pend_t = t;
             }
             TC_STAMP(9);
             fence_proxy_async_smem();
@@ -326,21 +376,19 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             named_barrier_sync(bar_id, 128);
             TC_STAMP(10);
 
-            // ---- store the out rows, refill the stage ----
-            if (v == 0) {
-                __nv_bfloat16* dst = a.out + (bos + t * kChunk) * a.token_stride + (int64_t)h * kD;
-                for (int i = 0; i < len; ++i) bulk_s2g(dst + i * a.token_stride, cs + kSmOut + i * kD * 2, kD * 2);
-                bulk_commit_group();
-                if (t + kTcStages < n_chunks) issue_load(t + kTcStages);
-            }
+            // ---- refill the stage just consumed ----
+            if (v == 0 && t + kTcStages < n_chunks) issue_load(t + kTcStages);
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) v_cur[i] = v_nxt[i];
             TC_STAMP(11);
 #ifdef FKDA_TC_TIMING
             if (blockIdx.x == 0 && threadIdx.x == 0 && t == 65) {
-                for (int i = 0; i < 13; ++i) a.status[15 + i] = (int)(stamps[i] - stamps[0]);
+                for (int i = 0; i < 23; ++i) a.status[15 + i] = (int)(stamps[i] - stamps[0]);
             }
 #endif
         }
         if (failed) break;
+        flush_out();
 
         // ---- final state: bf16, or the bf16 state widened to fp32 ----
         if (a.final_state != nullptr) {
@@ -366,7 +414,6 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
         ctl.abort_flag = 1;
         atomicExch(a.status, FKDA_ERR_DEVICE_STATUS);
     }
-    if (v == 0) bulk_wait_group<0>();  // this thread's out stores have fully completed
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) {
