@@ -10,9 +10,10 @@
 //        D2[V,16]  = u'^T[V,16] . INV^T           (M128 N16 K16)
 //        D3[V,16]  = U^T[V,16] . Mqk^T            (M128 N16 K16)
 //        DS[V,K]   = U^T[V,16] . kr[16,K]         (M128 N128 K16, MN-major B)
-//   * element-wise steps (bf16 roundings, beta, gate decay) by 128 threads, one per V row, reading the
+//   * element-wise steps (bf16 roundings, beta, gate decay) by 256 threads per chain: two threads per
+//     V row (= TMEM lane), each owning half of the tokens / half of the state columns, reading the
 //     accumulators with tcgen05.ld.
-// Three independent chains run per CTA (one warpgroup each) so that the tensor-core / barrier latency
+// Three independent chains run per CTA (eight warps each) so that the tensor-core / barrier latency
 // of one chain is covered by the element-wise work of the others.
 //
 // Numerics: steps B1-B7 of the reference's contract (tests/torch_ref.py:231-251; the reference's own
@@ -27,24 +28,25 @@ namespace fkda {
 using namespace sm100;
 
 // Profiling aid (off by default): with -DFKDA_TC_TIMING thread 0 of CTA 0 stores clock64() deltas of
-// the stages of its 64th chunk into the workspace header (ints 16..31).
+// the stages of its 64th chunk into the workspace header (ints 16..).
 #ifdef FKDA_TC_TIMING
-#define TC_STAMP(i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && t == 64) stamps[i] = clock64(); } while (0)
+#define TC_STAMP(i) do { if (stamp_on && t == 64) stamps[i] = clock64(); } while (0)
 #else
 #define TC_STAMP(i) do { } while (0)
 #endif
 
-constexpr int kTcChains = 3;    // chains (warpgroups) per CTA
-constexpr int kTcStages = 2;    // chunk records in flight per chain
+constexpr int kTcChains = 3;          // chains per CTA
+constexpr int kTcChainThreads = 256;  // threads per chain: 2 per V row
+constexpr int kTcStages = 2;          // chunk records in flight per chain
 constexpr int kTcTmemCols = 512;
 constexpr uint32_t kTcWaitNs = 2000000000u;
 
 // byte offsets inside one chain's shared-memory block
-constexpr int kSmS = 0;                                    // state, canonical K-major A operand [128, 128]
-constexpr int kSmStage = 32768;                            // kTcStages x (record + value tile)
-constexpr int kSmStageBytes = kTcRecord;                   // 13888
+constexpr int kSmS = 0;                                       // state, canonical K-major A operand [128, 128]
+constexpr int kSmStage = 32768;                               // kTcStages chunk records
+constexpr int kSmStageBytes = kTcRecord;                      // 13888
 constexpr int kSmA23 = kSmStage + kTcStages * kSmStageBytes;  // A operand of the 16-deep products [128, 16]
-constexpr int kSmChainBytes = kSmA23 + 4096;               // 64640
+constexpr int kSmChainBytes = kSmA23 + 4096;                  // 64640
 static_assert(kSmChainBytes % 128 == 0, "chain blocks stay 128-byte aligned");
 
 struct TcCtrl {
@@ -60,7 +62,7 @@ static_assert(kTcSmemBytes <= 232448, "exceeds the 227 KB shared-memory limit of
 // state element (v, k..k+7) lives at kc*2048 + (v/8)*128 + (v%8)*16   (kc = k/8)
 __device__ __forceinline__ int s_off(int v, int kc) { return kc * 2048 + (v >> 3) * 128 + (v & 7) * 16; }
 
-__global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPassArgs a) {
+__global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_kernel(TwoPassArgs a) {
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
     TcCtrl& ctl = *reinterpret_cast<TcCtrl*>(smem + kTcChains * kSmChainBytes);
@@ -68,16 +70,17 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
     // warp-uniform role indices (the shuffle makes the uniformity visible to the compiler, so the
     // single-thread tcgen05 issue below sits in warp-uniform control flow)
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
-    const int wg = warp >> 2;          // chain slot
-    const int wiw = warp & 3;          // warp within the warpgroup
+    const int c = warp >> 3;           // chain slot
+    const int wic = warp & 7;          // warp within the chain
+    const int half = wic >> 2;         // which half of the tokens / state columns this thread owns
     const int v = threadIdx.x & 127;   // state row = TMEM lane
-    uint8_t* cs = smem + wg * kSmChainBytes;
+    uint8_t* cs = smem + c * kSmChainBytes;
     volatile int* abort_flag = &ctl.abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int c = 0; c < kTcChains; ++c) {
-            for (int s = 0; s < kTcStages; ++s) mbar_init(&ctl.full[c][s], 1);
-            mbar_init(&ctl.mma[c], 1);
+        for (int i = 0; i < kTcChains; ++i) {
+            for (int s = 0; s < kTcStages; ++s) mbar_init(&ctl.full[i][s], 1);
+            mbar_init(&ctl.mma[i], 1);
         }
         ctl.abort_flag = 0;
         mbar_fence_init();
@@ -91,11 +94,11 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl.tmem_base;
-    // columns: DS of chain c at 128*c (128 wide), D1 of chain c at 384 + 32*c (32 wide; D2 reuses
-    // its first 16 columns and D3 its last 16 once D1 has been read)
+    // TMEM columns of chain c: DS at 128*c (128 wide; its first 16 columns also receive D2, which is
+    // consumed before DS is written), D1 at 384 + 32*c (u0 in 0-15, o0 in 16-31; D3 later replaces u0)
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t t_ds = tmem_base + 128u * wg;
-    const uint32_t t_d1 = tmem_base + 384u + 32u * wg;
+    const uint32_t t_ds = tmem_base + 128u * c;
+    const uint32_t t_d1 = tmem_base + 384u + 32u * c;
 
     constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, false, false);
     constexpr uint32_t idesc_n16 = make_idesc_bf16_f32(128, 16, false, false);
@@ -103,9 +106,10 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
 
     const uint32_t s_addr = smem_u32(cs + kSmS);
     const uint32_t a23_addr = smem_u32(cs + kSmA23);
-    const uint64_t s_desc0 = make_smem_desc(s_addr, 2048, 128);      // + 256 per K step of 16 (4096 B >> 4)
+    const uint64_t s_desc0 = make_smem_desc(s_addr, 2048, 128);  // + 256 per K step of 16 (4096 B >> 4)
     const uint64_t a23_desc = make_smem_desc(a23_addr, 2048, 128);
-    const int bar_id = 1 + wg;
+    uint8_t* const a23_mine = cs + kSmA23 + half * 2048 + (v >> 3) * 128 + (v & 7) * 16;
+    const int bar_id = 1 + c;
     const int64_t n_chains = a.N * a.H;
     uint32_t full_phase[kTcStages] = {0, 0};
     uint32_t mma_phase = 0;
@@ -116,9 +120,9 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
 
     while (!failed) {
         // ---- next chain from the work queue ----
-        if (v == 0) ctl.next_chain[wg] = atomicAdd(a.queue, 1);
-        named_barrier_sync(bar_id, 128);
-        const int64_t chain = ctl.next_chain[wg];
+        if ((threadIdx.x & 255) == 0) ctl.next_chain[c] = atomicAdd(a.queue, 1);
+        named_barrier_sync(bar_id, kTcChainThreads);
+        const int64_t chain = ctl.next_chain[c];
         if (chain >= n_chains) break;
         const int64_t n = chain / a.H;
         const int h = (int)(chain - n * a.H);
@@ -133,34 +137,40 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             seq_len = a.T;
             tile_base = n * ((a.T + kChunk - 1) / kChunk);
         }
-        const int64_t n_chunks = (seq_len + kChunk - 1) / kChunk;
+        const int n_chunks = (int)((seq_len + kChunk - 1) / kChunk);
         const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
-        const int64_t st_off = (n * a.H + h) * (int64_t)(kD * kD) + (int64_t)v * kD;
+        // this thread's half row of the state: columns 64*half .. 64*half+63 of row v
+        const int64_t st_off = (n * a.H + h) * (int64_t)(kD * kD) + (int64_t)v * kD + half * 64;
 
-        auto issue_load = [&](int64_t t) {  // one thread: the record of chunk t into stage t % kTcStages
-            const int s = (int)(t % kTcStages);
-            mbar_arrive_expect_tx(&ctl.full[wg][s], (uint32_t)kTcRecord);
-            bulk_g2s(cs + kSmStage + s * kSmStageBytes, rec_base + t * (int64_t)kTcRecord, kTcRecord,
-                     &ctl.full[wg][s]);
+#ifdef FKDA_TC_TIMING
+        const bool stamp_on = (chain == 0) && (threadIdx.x & 255) == 0;
+#endif
+        auto issue_load = [&](int t) {  // one thread: the record of chunk t into stage t % kTcStages
+            const int s = t % kTcStages;
+            mbar_arrive_expect_tx(&ctl.full[c][s], (uint32_t)kTcRecord);
+            bulk_g2s(cs + kSmStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[c][s]);
         };
-        if (v == 0) {
-            for (int64_t t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
+        if ((threadIdx.x & 255) == 0) {
+            for (int t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
         }
-        // value column of this thread for chunk t: rows (2i, 2i+1) packed as bf16x2, zero past the end;
-        // fetched straight from global memory one chunk ahead (64 contiguous bytes per warp and row)
-        const unsigned short* vcol = reinterpret_cast<const unsigned short*>(a.v) + bos * a.token_stride +
+        // value column v of this thread's 8 tokens (8*half ..) of chunk t, fetched straight from global
+        // memory one chunk ahead (64 contiguous bytes per warp and row); the raw 16-bit values are kept
+        // apart until they are used, so the loads stay in flight
+        const int64_t tstride = a.token_stride;
+        const unsigned short* vcol = reinterpret_cast<const unsigned short*>(a.v) + (bos + 8 * half) * tstride +
                                      (int64_t)h * kD + v;
-        // (the raw 16-bit values are kept apart until they are used, so the loads stay in flight)
-        auto load_v = [&](int64_t t, unsigned short (&dst)[kChunk]) {
-            const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
-            const unsigned short* p = vcol + t * kChunk * a.token_stride;
+        unsigned short* ocol = reinterpret_cast<unsigned short*>(a.out) + (bos + 8 * half) * tstride +
+                               (int64_t)h * kD + v;
+        auto load_v = [&](int t, unsigned short (&dst)[8]) {
+            const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk) - 8 * half;  // my valid rows
+            const unsigned short* p = vcol + (int64_t)t * kChunk * tstride;
 #pragma unroll
-            for (int i = 0; i < kChunk; ++i) {
+            for (int i = 0; i < 8; ++i) {
                 dst[i] = (i < len) ? __ldg(p) : (unsigned short)0;
-                p += a.token_stride;
+                p += tstride;
             }
         };
-        unsigned short v_cur[kChunk], v_nxt[kChunk];
+        unsigned short v_cur[8], v_nxt[8];
         if (n_chunks > 0) load_v(0, v_cur);
 
         // ---- initial state into the canonical A-operand layout (fp32 rounded to bf16) ----
@@ -168,246 +178,235 @@ __global__ void __launch_bounds__(kTcChains * 128, 1) recurrence_tc_kernel(TwoPa
             if (a.state_fp32) {
                 const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.initial_state) + st_off);
 #pragma unroll 4
-                for (int kc = 0; kc < 16; ++kc) {
-                    const float4 x = src[2 * kc], y = src[2 * kc + 1];
-                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc)) =
+                for (int q = 0; q < 8; ++q) {
+                    const float4 x = src[2 * q], y = src[2 * q + 1];
+                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, 8 * half + q)) =
                         make_uint4(pack_bf2(x.x, x.y), pack_bf2(x.z, x.w), pack_bf2(y.x, y.y), pack_bf2(y.z, y.w));
                 }
             } else {
                 const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.initial_state) + st_off);
 #pragma unroll 4
-                for (int kc = 0; kc < 16; ++kc) *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc)) = src[kc];
+                for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, 8 * half + q)) = src[q];
             }
         } else {
 #pragma unroll 4
-            for (int kc = 0; kc < 16; ++kc) *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc)) = make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, 8 * half + q)) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
-        named_barrier_sync(bar_id, 128);
+        named_barrier_sync(bar_id, kTcChainThreads);
 
-        // out rows of the previous chunk, finished while the next chunk's first MMA runs
-        uint32_t o_pend[8];
-        int64_t o_pend_t = -1;
+        // out rows of the previous chunk (this thread's 8 tokens), stored while the next chunk's first
+        // MMA runs
+        uint32_t o_pend[4];
+        int o_pend_t = -1;
         auto flush_out = [&]() {
             if (o_pend_t < 0) return;
-            const int len = (int)min((int64_t)kChunk, seq_len - o_pend_t * kChunk);
-            unsigned short* dst = reinterpret_cast<unsigned short*>(a.out) +
-                                  (bos + o_pend_t * kChunk) * a.token_stride + (int64_t)h * kD + v;
+            const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)o_pend_t * kChunk) - 8 * half;
+            unsigned short* dst = ocol + (int64_t)o_pend_t * kChunk * tstride;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
                 if (2 * i < len) *dst = (unsigned short)(o_pend[i] & 0xffffu);
-                dst += a.token_stride;
+                dst += tstride;
                 if (2 * i + 1 < len) *dst = (unsigned short)(o_pend[i] >> 16);
-                dst += a.token_stride;
+                dst += tstride;
             }
             o_pend_t = -1;
         };
 
-        for (int64_t t = 0; t < n_chunks; ++t) {
-            const int s = (int)(t % kTcStages);
+        for (int t = 0; t < n_chunks; ++t) {
+            const int s = t % kTcStages;
             uint8_t* st = cs + kSmStage + s * kSmStageBytes;
             const uint32_t st_addr = smem_u32(st);
 
             TC_STAMP(8);
             // ---- operands of chunk t have landed ----
-            if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.full[c][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
             full_phase[s] ^= 1u;
             TC_STAMP(0);
-#ifdef FKDA_TC_TIMING
-            if (blockIdx.x == 0 && threadIdx.x == 0 && t == 65) stamps[12] = clock64();
-#endif
 
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
-            if (wiw == 0) {
+            if (wic == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
                     const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, 512, 128);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         umma_ss(t_d1, s_desc0 + (uint64_t)(j * 256), bd0 + (uint64_t)(j * 64), idesc_n32, j > 0 ? 1u : 0u);
-                    umma_commit(&ctl.mma[wg]);
+                    umma_commit(&ctl.mma[c]);
                 }
                 __syncwarp();
             }
             TC_STAMP(1);
             // work off the critical path while the MMA runs
             flush_out();
-            TC_STAMP(13);
             if (t + 1 < n_chunks) load_v(t + 1, v_nxt);
-            TC_STAMP(14);
-            const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
-            uint32_t bpk[8];
-#pragma unroll
-            for (int i4 = 0; i4 < 4; ++i4) {
-                const float4 b = bp[i4];
-                bpk[2 * i4] = pack_bf2(b.x, b.y);  // exact: the record holds bf16-rounded values
-                bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
+            uint32_t bpk[4];  // bf16x2 pairs of sigmoid(beta) for my 8 tokens (the record holds bf16-rounded values)
+            {
+                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta) + 2 * half;
+                const float4 b0 = bp[0], b1 = bp[1];
+                bpk[0] = pack_bf2(b0.x, b0.y); bpk[1] = pack_bf2(b0.z, b0.w);
+                bpk[2] = pack_bf2(b1.x, b1.y); bpk[3] = pack_bf2(b1.z, b1.w);
             }
-            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[c], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(2);
 
-            // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand; keep bf(o0) ----
-            uint32_t ob[8];
+            // ---- u' = (v (-) bf(u0)) (*) bf(beta) for my 8 tokens -> my half of the A operand ----
             {
-                uint32_t r[32];
-                tmem_ld32(t_d1 + lane_sel, r);
+                uint32_t r[8];
+                tmem_ld8(t_d1 + 8 * half + lane_sel, r);
                 tmem_wait_ld();
-                uint32_t up[8];
+                uint32_t up[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < 4; ++i) {
                     const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
                     const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
                     up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
-                    ob[i] = pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1]));
                 }
-                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                *reinterpret_cast<uint4*>(ap) = make_uint4(up[0], up[1], up[2], up[3]);
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(up[4], up[5], up[6], up[7]);
+                *reinterpret_cast<uint4*>(a23_mine) = make_uint4(up[0], up[1], up[2], up[3]);
             }
             TC_STAMP(3);
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_barrier_sync(bar_id, 128);
+            named_barrier_sync(bar_id, kTcChainThreads);
             TC_STAMP(4);
 
-            // ---- MMA2: D2[V,16] = u'^T . INV^T ----
-            if (wiw == 0) {
+            // ---- MMA2: D2[V,16] = u'^T . INV^T  (into the first 16 DS columns) ----
+            if (wic == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
-                    umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
-                    umma_commit(&ctl.mma[wg]);
+                    umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
+                    umma_commit(&ctl.mma[c]);
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[c], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(5);
             {
-                uint32_t r[16];
-                tmem_ld16(t_d1 + lane_sel, r);
+                uint32_t r[8];
+                tmem_ld8(t_ds + 8 * half + lane_sel, r);
                 tmem_wait_ld();
-                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                uint32_t p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
+                *reinterpret_cast<uint4*>(a23_mine) =
+                    make_uint4(pack_bf2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                               pack_bf2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                               pack_bf2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                               pack_bf2(__uint_as_float(r[6]), __uint_as_float(r[7])));
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_barrier_sync(bar_id, 128);
+            named_barrier_sync(bar_id, kTcChainThreads);
             TC_STAMP(6);
 
-            // ---- MMA3: D3[V,16] = U^T . Mqk^T ;  DS[V,K] = U^T . kr ----
-            if (wiw == 0) {
+            // ---- MMA3: D3[V,16] = U^T . Mqk^T (over the dead u0 columns);  DS[V,K] = U^T . kr ----
+            if (wic == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
-                    umma_ss(t_d1 + 16, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
+                    umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
                     umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcKr, 2048, 128), idesc_ds, 0u);
-                    umma_commit(&ctl.mma[wg]);
+                    umma_commit(&ctl.mma[c]);
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[c], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(7);
 
-            // ---- S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])), TMEM loads one batch ahead;
-            //      out = bf(o0) (+) bf(Mqk U) is only formed here, its stores wait for the next MMA1 ----
-            auto update_cols = [&](int cb, const uint32_t (&r)[32]) {
+            // ---- my 64 state columns: S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])), TMEM loads one
+            //      batch of 16 columns ahead; out = bf(o0) (+) bf(Mqk U) for my 8 tokens is formed here and
+            //      stored while the next chunk's first MMA runs ----
+            auto update_cols = [&](int b, const uint32_t (&r)[16]) {
                 // all loads of the batch first: the stores below may alias them as far as the compiler knows
-                const float4* ep = reinterpret_cast<const float4*>(st + kTcEt) + cb * 8;
-                uint4 sv[4];
-                float4 e[8];
+                const int kc0 = 8 * half + 2 * b;
+                const float4* ep = reinterpret_cast<const float4*>(st + kTcEt) + 2 * kc0;
+                uint4 sv[2];
+                float4 e[4];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) sv[q4] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, cb * 4 + q4));
+                for (int q = 0; q < 2; ++q) sv[q] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, kc0 + q));
 #pragma unroll
-                for (int q = 0; q < 8; ++q) e[q] = ep[q];
+                for (int q = 0; q < 4; ++q) e[q] = ep[q];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const float4 e0 = e[2 * q4], e1 = e[2 * q4 + 1];
-                    const uint32_t* rr = r + q4 * 8;
+                for (int q = 0; q < 2; ++q) {
+                    const float4 e0 = e[2 * q], e1 = e[2 * q + 1];
+                    const uint32_t* rr = r + q * 8;
                     uint4 nv;
-                    nv.x = pack_bf2(__fmaf_rn(bf_lo(sv[q4].x), e0.x, __uint_as_float(rr[0])),
-                                    __fmaf_rn(bf_hi(sv[q4].x), e0.y, __uint_as_float(rr[1])));
-                    nv.y = pack_bf2(__fmaf_rn(bf_lo(sv[q4].y), e0.z, __uint_as_float(rr[2])),
-                                    __fmaf_rn(bf_hi(sv[q4].y), e0.w, __uint_as_float(rr[3])));
-                    nv.z = pack_bf2(__fmaf_rn(bf_lo(sv[q4].z), e1.x, __uint_as_float(rr[4])),
-                                    __fmaf_rn(bf_hi(sv[q4].z), e1.y, __uint_as_float(rr[5])));
-                    nv.w = pack_bf2(__fmaf_rn(bf_lo(sv[q4].w), e1.z, __uint_as_float(rr[6])),
-                                    __fmaf_rn(bf_hi(sv[q4].w), e1.w, __uint_as_float(rr[7])));
-                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, cb * 4 + q4)) = nv;
+                    nv.x = pack_bf2(__fmaf_rn(bf_lo(sv[q].x), e0.x, __uint_as_float(rr[0])),
+                                    __fmaf_rn(bf_hi(sv[q].x), e0.y, __uint_as_float(rr[1])));
+                    nv.y = pack_bf2(__fmaf_rn(bf_lo(sv[q].y), e0.z, __uint_as_float(rr[2])),
+                                    __fmaf_rn(bf_hi(sv[q].y), e0.w, __uint_as_float(rr[3])));
+                    nv.z = pack_bf2(__fmaf_rn(bf_lo(sv[q].z), e1.x, __uint_as_float(rr[4])),
+                                    __fmaf_rn(bf_hi(sv[q].z), e1.y, __uint_as_float(rr[5])));
+                    nv.w = pack_bf2(__fmaf_rn(bf_lo(sv[q].w), e1.z, __uint_as_float(rr[6])),
+                                    __fmaf_rn(bf_hi(sv[q].w), e1.w, __uint_as_float(rr[7])));
+                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc0 + q)) = nv;
                 }
             };
             {
-                uint32_t r3[16], ra[32], rb[32];
-                tmem_ld32(t_ds + lane_sel, ra);
-                tmem_ld16(t_d1 + 16 + lane_sel, r3);
-                TC_STAMP(16);
+                uint32_t ra[16], rb[16], r3[8], ro[8];
+                const uint32_t ds_mine = t_ds + 64 * half + lane_sel;
+                tmem_ld16(ds_mine, ra);
+                tmem_ld8(t_d1 + 8 * half + lane_sel, r3);
+                tmem_ld8(t_d1 + 16 + 8 * half + lane_sel, ro);
                 tmem_wait_ld();
-                TC_STAMP(17);
-                tmem_ld32(t_ds + 32 + lane_sel, rb);
-                TC_STAMP(18);
+                tmem_ld16(ds_mine + 16, rb);
                 update_cols(0, ra);
-                TC_STAMP(19);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    o_pend[i] = bf2_add(pack_bf2(__uint_as_float(ro[2 * i]), __uint_as_float(ro[2 * i + 1])),
+                                        pack_bf2(__uint_as_float(r3[2 * i]), __uint_as_float(r3[2 * i + 1])));
+                o_pend_t = t;
                 tmem_wait_ld();
-                TC_STAMP(20);
-                tmem_ld32(t_ds + 64 + lane_sel, ra);
+                tmem_ld16(ds_mine + 32, ra);
                 update_cols(1, rb);
-                TC_STAMP(21);
                 tmem_wait_ld();
-                TC_STAMP(22);
-                tmem_ld32(t_ds + 96 + lane_sel, rb);
+                tmem_ld16(ds_mine + 48, rb);
                 update_cols(2, ra);
                 tmem_wait_ld();
                 update_cols(3, rb);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    o_pend[i] = bf2_add(ob[i], pack_bf2(__uint_as_float(r3[2 * i]), __uint_as_float(r3[2 * i + 1])));
-                o_pend_t = t;
             }
             TC_STAMP(9);
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_barrier_sync(bar_id, 128);
+            named_barrier_sync(bar_id, kTcChainThreads);
             TC_STAMP(10);
 
             // ---- refill the stage just consumed ----
-            if (v == 0 && t + kTcStages < n_chunks) issue_load(t + kTcStages);
+            if ((threadIdx.x & 255) == 0 && t + kTcStages < n_chunks) issue_load(t + kTcStages);
 #pragma unroll
-            for (int i = 0; i < kChunk; ++i) v_cur[i] = v_nxt[i];
+            for (int i = 0; i < 8; ++i) v_cur[i] = v_nxt[i];
             TC_STAMP(11);
 #ifdef FKDA_TC_TIMING
-            if (blockIdx.x == 0 && threadIdx.x == 0 && t == 65) {
-                for (int i = 0; i < 23; ++i) a.status[15 + i] = (int)(stamps[i] - stamps[0]);
+            if (stamp_on && t == 65) {
+                stamps[12] = clock64();
+                for (int i = 0; i < 13; ++i) a.status[15 + i] = (int)(stamps[i] - stamps[0]);
             }
 #endif
         }
         if (failed) break;
         flush_out();
 
-        // ---- final state: bf16, or the bf16 state widened to fp32 ----
+        // ---- final state (my 64 columns): bf16, or the bf16 state widened to fp32 ----
         if (a.final_state != nullptr) {
             if (a.state_fp32) {
                 float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.final_state) + st_off);
 #pragma unroll 4
-                for (int kc = 0; kc < 16; ++kc) {
-                    const uint4 sv = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, kc));
-                    dst[2 * kc] = make_float4(bf_lo(sv.x), bf_hi(sv.x), bf_lo(sv.y), bf_hi(sv.y));
-                    dst[2 * kc + 1] = make_float4(bf_lo(sv.z), bf_hi(sv.z), bf_lo(sv.w), bf_hi(sv.w));
+                for (int q = 0; q < 8; ++q) {
+                    const uint4 sv = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, 8 * half + q));
+                    dst[2 * q] = make_float4(bf_lo(sv.x), bf_hi(sv.x), bf_lo(sv.y), bf_hi(sv.y));
+                    dst[2 * q + 1] = make_float4(bf_lo(sv.z), bf_hi(sv.z), bf_lo(sv.w), bf_hi(sv.w));
                 }
             } else {
                 uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.final_state) + st_off);
 #pragma unroll 4
-                for (int kc = 0; kc < 16; ++kc) dst[kc] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, kc));
+                for (int q = 0; q < 8; ++q) dst[q] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, 8 * half + q));
             }
         }
         // all rows exported and all operand reads done before the next chain overwrites S / the stages
-        named_barrier_sync(bar_id, 128);
+        named_barrier_sync(bar_id, kTcChainThreads);
     }
 
     if (failed) {
@@ -457,7 +456,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         int64_t ctas = (chains + kTcChains - 1) / kTcChains;
         if (ctas > sms) ctas = sms;
         if (ctas < 1) ctas = 1;
-        recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a);
+        recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * kTcChainThreads, kTcSmemBytes, stream>>>(a);
         ++launches;
     }
     if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
