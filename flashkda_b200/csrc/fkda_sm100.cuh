@@ -108,6 +108,26 @@ __device__ __forceinline__ void bulk_wait_group() {
     asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// --------------------------------------- tiled TMA copies through a tensor map ----
+// 3-D tile, global -> shared (destination 128-byte aligned), completion in bytes on an mbarrier.
+// Coordinates are innermost first; the innermost one times the element size must be a multiple of 16.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
+}
+// 3-D tile, shared -> global, tracked by the issuing thread's bulk async-group; rows outside the
+// tensor are clipped.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, int c0, int c1, int c2, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(tmap),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
 // ------------------------------------------------------------------- TMEM ----
 // One full warp allocates `n_cols` (power of two, 32..512) columns; the base address is written to
 // shared memory.  The same warp frees them before the CTA exits.

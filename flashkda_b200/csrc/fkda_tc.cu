@@ -1,23 +1,26 @@
 // Tensor-core two-pass KDA forward for sm_100a: the token-parallel prepare kernel writes per-chunk
 // operand records already laid out as tcgen05 (UMMA) shared-memory operands; a persistent
 // recurrence kernel walks the chunks of each (sequence, head) chain with
-//   * one bulk asynchronous copy (TMA engine) per chunk record, double buffered on mbarriers; value
-//     columns prefetched into registers one chunk ahead, out rows stored from registers,
-//   * the [128,128] bf16 state resident in shared memory as the A operand of the state contraction,
-//   * all contractions on tcgen05.mma with fp32 accumulators in tensor memory, in the transposed
-//     formulation that makes V = 128 the MMA M dimension:
-//        D1[V,32]  = S[V,K] . [kd; qd]^T          (8 x M128 N32 K16)
-//        D2[V,16]  = u'^T[V,16] . INV^T           (M128 N16 K16)
-//        D3[V,16]  = U^T[V,16] . Mqk^T            (M128 N16 K16)
-//        DS[V,K]   = U^T[V,16] . kr[16,K]         (M128 N128 K16, MN-major B)
-//   * element-wise steps (bf16 roundings, beta, gate decay) by 256 threads per chain: two threads per
-//     V row (= TMEM lane), each owning half of the tokens / half of the state columns, reading the
-//     accumulators with tcgen05.ld.
-// Three independent chains run per CTA (eight warps each) so that the tensor-core / barrier latency
+//   * per chunk one bulk asynchronous copy of the record plus one tiled TMA load (tensor map) of the
+//     [16,128] value tile, double buffered on mbarriers; out tiles leave through a tiled TMA store,
+//   * all contractions on tcgen05.mma with fp32 accumulators in tensor memory (M = 128 always):
+//        D1[V,32]   = S[V,K] . [kd; qd]^T         (8 x M128 N32 K16; A = S^T tile read MN-major)
+//        D2[V,16]   = u'^T[V,16] . INV^T          (M128 N16 K16)
+//        D3[V,16]   = U^T[V,16] . Mqk^T           (M128 N16 K16)
+//        DST[K,V]   = kr^T[K,16] . U[16,V]        (M128 N128 K16; the state update, TRANSPOSED: lane = k)
+//   * the bf16 state held twice: in the registers of its owner threads (thread k owns S[:,k], 64 packed
+//     registers) for the element-wise update S[v,k] = bf(fma(S[v,k], E_tot[k], DST[k,v])) -- one gate
+//     scalar per thread, no shared-memory reads -- and as the S^T tile in shared memory (written once
+//     per chunk) that the next chunk's first MMA reads as its A operand,
+//   * the other element-wise steps (bf16 roundings, beta) by the same 128 threads in the other
+//     orientation (thread v = TMEM lane v of D1/D2/D3), reading accumulators with tcgen05.ld.
+// Three independent chains run per CTA (one warpgroup each) so that the tensor-core / barrier latency
 // of one chain is covered by the element-wise work of the others.
 //
 // Numerics: steps B1-B7 of the reference's contract (tests/torch_ref.py:231-251; the reference's own
 // recurrence is csrc/smxx/fwd_kernel2.cuh:434-742, built on mma.sync with register transposes).
+#include <cuda.h>
+
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
 #include "fkda_prepare.cuh"
@@ -28,25 +31,27 @@ namespace fkda {
 using namespace sm100;
 
 // Profiling aid (off by default): with -DFKDA_TC_TIMING thread 0 of CTA 0 stores clock64() deltas of
-// the stages of its 64th chunk into the workspace header (ints 16..).
+// the stages of its 64th chunk into the workspace header (ints 16..31).
 #ifdef FKDA_TC_TIMING
 #define TC_STAMP(i) do { if (stamp_on && t == 64) stamps[i] = clock64(); } while (0)
 #else
 #define TC_STAMP(i) do { } while (0)
 #endif
 
-constexpr int kTcChains = 3;          // chains per CTA
-constexpr int kTcChainThreads = 256;  // threads per chain: 2 per V row
-constexpr int kTcStages = 2;          // chunk records in flight per chain
+constexpr int kTcChains = 3;    // chains (warpgroups) per CTA
+constexpr int kTcStages = 2;    // chunk records in flight per chain
 constexpr int kTcTmemCols = 512;
 constexpr uint32_t kTcWaitNs = 2000000000u;
 
 // byte offsets inside one chain's shared-memory block
-constexpr int kSmS = 0;                                       // state, canonical K-major A operand [128, 128]
-constexpr int kSmStage = 32768;                               // kTcStages chunk records
-constexpr int kSmStageBytes = kTcRecord;                      // 13888
-constexpr int kSmA23 = kSmStage + kTcStages * kSmStageBytes;  // A operand of the 16-deep products [128, 16]
-constexpr int kSmChainBytes = kSmA23 + 4096;                  // 64640
+constexpr int kSmS = 0;                                    // S^T tile: the state as MN-major A operand [v, k]
+constexpr int kSmStage = 32768;                            // kTcStages chunk records
+constexpr int kSmStageBytes = kTcRecord;                   // 13888
+constexpr int kSmV = kSmStage + kTcStages * kSmStageBytes;    // kTcStages value tiles [16][128] bf16 (60544)
+constexpr int kSmA23 = kSmV + kTcStages * 4096;               // A operand of the 16-deep products [128, 16]
+constexpr int kSmOut = kSmA23 + 4096;                         // out tile [16][128] bf16
+constexpr int kSmChainBytes = kSmOut + 4096;                  // 76928
+static_assert(kSmV % 128 == 0 && kSmOut % 128 == 0, "TMA tiles are 128-byte aligned");
 static_assert(kSmChainBytes % 128 == 0, "chain blocks stay 128-byte aligned");
 
 struct TcCtrl {
@@ -59,10 +64,17 @@ struct TcCtrl {
 constexpr int kTcSmemBytes = kTcChains * kSmChainBytes + (int)sizeof(TcCtrl) + 128;
 static_assert(kTcSmemBytes <= 232448, "exceeds the 227 KB shared-memory limit of a CTA");
 
-// state element (v, k..k+7) lives at kc*2048 + (v/8)*128 + (v%8)*16   (kc = k/8)
-__device__ __forceinline__ int s_off(int v, int kc) { return kc * 2048 + (v >> 3) * 128 + (v & 7) * 16; }
+// S^T tile, MN-major canonical A operand [M = v, K = k]: elements (v..v+7, k) are the 16 bytes at
+// (k/8)*2048 + (v/8)*128 + (k%8)*16
+__device__ __forceinline__ int sT_off(int k, int vg) { return (k >> 3) * 2048 + vg * 128 + (k & 7) * 16; }
 
-__global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_kernel(TwoPassArgs a) {
+// Tensor maps over v and out viewed as [token][head][128] bf16 (box = 16 tokens x 1 head x 128).
+struct alignas(64) TcMaps {
+    CUtensorMap v, out;
+};
+
+__global__ void __launch_bounds__(kTcChains * 128, 1)
+recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constant__ TcMaps maps) {
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
     TcCtrl& ctl = *reinterpret_cast<TcCtrl*>(smem + kTcChains * kSmChainBytes);
@@ -70,17 +82,16 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
     // warp-uniform role indices (the shuffle makes the uniformity visible to the compiler, so the
     // single-thread tcgen05 issue below sits in warp-uniform control flow)
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
-    const int c = warp >> 3;           // chain slot
-    const int wic = warp & 7;          // warp within the chain
-    const int half = wic >> 2;         // which half of the tokens / state columns this thread owns
+    const int wg = warp >> 2;          // chain slot
+    const int wiw = warp & 3;          // warp within the warpgroup
     const int v = threadIdx.x & 127;   // state row = TMEM lane
-    uint8_t* cs = smem + c * kSmChainBytes;
+    uint8_t* cs = smem + wg * kSmChainBytes;
     volatile int* abort_flag = &ctl.abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kTcChains; ++i) {
-            for (int s = 0; s < kTcStages; ++s) mbar_init(&ctl.full[i][s], 1);
-            mbar_init(&ctl.mma[i], 1);
+        for (int c = 0; c < kTcChains; ++c) {
+            for (int s = 0; s < kTcStages; ++s) mbar_init(&ctl.full[c][s], 1);
+            mbar_init(&ctl.mma[c], 1);
         }
         ctl.abort_flag = 0;
         mbar_fence_init();
@@ -94,22 +105,21 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl.tmem_base;
-    // TMEM columns of chain c: DS at 128*c (128 wide; its first 16 columns also receive D2, which is
-    // consumed before DS is written), D1 at 384 + 32*c (u0 in 0-15, o0 in 16-31; D3 later replaces u0)
+    // columns: DST of chain c at 128*c (128 wide; its first 16 columns also receive D2, which is consumed
+    // before DST is written), D1 at 384 + 32*c (u0 in 0-15, o0 in 16-31; D3 later replaces u0)
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t t_ds = tmem_base + 128u * c;
-    const uint32_t t_d1 = tmem_base + 384u + 32u * c;
+    const uint32_t t_ds = tmem_base + 128u * wg;
+    const uint32_t t_d1 = tmem_base + 384u + 32u * wg;
 
-    constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, false, false);
+    constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, true, false);    // A = S^T tile, MN-major
     constexpr uint32_t idesc_n16 = make_idesc_bf16_f32(128, 16, false, false);
-    constexpr uint32_t idesc_ds = make_idesc_bf16_f32(128, 128, false, true);
+    constexpr uint32_t idesc_dst = make_idesc_bf16_f32(128, 128, true, false);   // A = kr tile, MN-major
 
     const uint32_t s_addr = smem_u32(cs + kSmS);
     const uint32_t a23_addr = smem_u32(cs + kSmA23);
-    const uint64_t s_desc0 = make_smem_desc(s_addr, 2048, 128);  // + 256 per K step of 16 (4096 B >> 4)
+    const uint64_t s_desc0 = make_smem_desc(s_addr, 2048, 128);      // LBO: k groups, SBO: v groups; + 256 per K step
     const uint64_t a23_desc = make_smem_desc(a23_addr, 2048, 128);
-    uint8_t* const a23_mine = cs + kSmA23 + half * 2048 + (v >> 3) * 128 + (v & 7) * 16;
-    const int bar_id = 1 + c;
+    const int bar_id = 1 + wg;
     const int64_t n_chains = a.N * a.H;
     uint32_t full_phase[kTcStages] = {0, 0};
     uint32_t mma_phase = 0;
@@ -120,9 +130,9 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
 
     while (!failed) {
         // ---- next chain from the work queue ----
-        if ((threadIdx.x & 255) == 0) ctl.next_chain[c] = atomicAdd(a.queue, 1);
-        named_barrier_sync(bar_id, kTcChainThreads);
-        const int64_t chain = ctl.next_chain[c];
+        if (v == 0) ctl.next_chain[wg] = atomicAdd(a.queue, 1);
+        named_barrier_sync(bar_id, 128);
+        const int64_t chain = ctl.next_chain[wg];
         if (chain >= n_chains) break;
         const int64_t n = chain / a.H;
         const int h = (int)(chain - n * a.H);
@@ -139,80 +149,50 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
         }
         const int n_chunks = (int)((seq_len + kChunk - 1) / kChunk);
         const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
-        // this thread's half row of the state: columns 64*half .. 64*half+63 of row v
-        const int64_t st_off = (n * a.H + h) * (int64_t)(kD * kD) + (int64_t)v * kD + half * 64;
-
+        // thread k = v owns state column k: element S[vv][k] of this chain sits at st_base + vv * 128
+        const int64_t st_base = (n * a.H + h) * (int64_t)(kD * kD) + v;
 #ifdef FKDA_TC_TIMING
-        const bool stamp_on = (chain == 0) && (threadIdx.x & 255) == 0;
+        const bool stamp_on = (chain == 0) && v == 0;
 #endif
+
         auto issue_load = [&](int t) {  // one thread: the record of chunk t into stage t % kTcStages
             const int s = t % kTcStages;
-            mbar_arrive_expect_tx(&ctl.full[c][s], (uint32_t)kTcRecord);
-            bulk_g2s(cs + kSmStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[c][s]);
+            mbar_arrive_expect_tx(&ctl.full[wg][s], (uint32_t)(kTcRecord + kChunk * kD * 2));
+            bulk_g2s(cs + kSmStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[wg][s]);
+            // rows past the end of the tensor arrive as zeros; rows of the next sequence are never used
+            tma_load_3d(cs + kSmV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[wg][s]);
         };
-        if ((threadIdx.x & 255) == 0) {
+        if (v == 0) {
             for (int t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
         }
-        // value column v of this thread's 8 tokens (8*half ..) of chunk t, fetched straight from global
-        // memory one chunk ahead (64 contiguous bytes per warp and row); the raw 16-bit values are kept
-        // apart until they are used, so the loads stay in flight
         const int64_t tstride = a.token_stride;
-        const unsigned short* vcol = reinterpret_cast<const unsigned short*>(a.v) + (bos + 8 * half) * tstride +
-                                     (int64_t)h * kD + v;
-        unsigned short* ocol = reinterpret_cast<unsigned short*>(a.out) + (bos + 8 * half) * tstride +
-                               (int64_t)h * kD + v;
-        auto load_v = [&](int t, unsigned short (&dst)[8]) {
-            const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk) - 8 * half;  // my valid rows
-            const unsigned short* p = vcol + (int64_t)t * kChunk * tstride;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                dst[i] = (i < len) ? __ldg(p) : (unsigned short)0;
-                p += tstride;
-            }
-        };
-        unsigned short v_cur[8], v_nxt[8];
-        if (n_chunks > 0) load_v(0, v_cur);
+        unsigned short* ocol = reinterpret_cast<unsigned short*>(a.out) + bos * tstride + (int64_t)h * kD + v;
 
-        // ---- initial state into the canonical A-operand layout (fp32 rounded to bf16) ----
+        // ---- initial state: column k of S into registers (pairs over v) and into the S^T tile ----
+        uint32_t sreg[64];
         if (a.initial_state != nullptr) {
             if (a.state_fp32) {
-                const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.initial_state) + st_off);
-#pragma unroll 4
-                for (int q = 0; q < 8; ++q) {
-                    const float4 x = src[2 * q], y = src[2 * q + 1];
-                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, 8 * half + q)) =
-                        make_uint4(pack_bf2(x.x, x.y), pack_bf2(x.z, x.w), pack_bf2(y.x, y.y), pack_bf2(y.z, y.w));
-                }
+                const float* src = reinterpret_cast<const float*>(a.initial_state) + st_base;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) sreg[i] = pack_bf2(src[(2 * i) * kD], src[(2 * i + 1) * kD]);
             } else {
-                const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.initial_state) + st_off);
-#pragma unroll 4
-                for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, 8 * half + q)) = src[q];
+                const unsigned short* src = reinterpret_cast<const unsigned short*>(a.initial_state) + st_base;
+#pragma unroll
+                for (int i = 0; i < 64; ++i)
+                    sreg[i] = (uint32_t)src[(2 * i) * kD] | ((uint32_t)src[(2 * i + 1) * kD] << 16);
             }
         } else {
-#pragma unroll 4
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, 8 * half + q)) = make_uint4(0, 0, 0, 0);
-        }
-        fence_proxy_async_smem();
-        named_barrier_sync(bar_id, kTcChainThreads);
-
-        // out rows of the previous chunk (this thread's 8 tokens), stored while the next chunk's first
-        // MMA runs
-        uint32_t o_pend[4];
-        int o_pend_t = -1;
-        auto flush_out = [&]() {
-            if (o_pend_t < 0) return;
-            const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)o_pend_t * kChunk) - 8 * half;
-            unsigned short* dst = ocol + (int64_t)o_pend_t * kChunk * tstride;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (2 * i < len) *dst = (unsigned short)(o_pend[i] & 0xffffu);
-                dst += tstride;
-                if (2 * i + 1 < len) *dst = (unsigned short)(o_pend[i] >> 16);
-                dst += tstride;
-            }
-            o_pend_t = -1;
-        };
+            for (int i = 0; i < 64; ++i) sreg[i] = 0u;
+        }
+#pragma unroll
+        for (int vg = 0; vg < 16; ++vg)
+            *reinterpret_cast<uint4*>(cs + kSmS + sT_off(v, vg)) =
+                make_uint4(sreg[4 * vg], sreg[4 * vg + 1], sreg[4 * vg + 2], sreg[4 * vg + 3]);
+        fence_proxy_async_smem();
+        named_barrier_sync(bar_id, 128);
+
+        __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kSmOut);
 
         for (int t = 0; t < n_chunks; ++t) {
             const int s = t % kTcStages;
@@ -221,163 +201,169 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
 
             TC_STAMP(8);
             // ---- operands of chunk t have landed ----
-            if (!mbar_wait_bounded(&ctl.full[c][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
             full_phase[s] ^= 1u;
             TC_STAMP(0);
 
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
-            if (wic == 0) {
+            if (wiw == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
                     const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, 512, 128);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         umma_ss(t_d1, s_desc0 + (uint64_t)(j * 256), bd0 + (uint64_t)(j * 64), idesc_n32, j > 0 ? 1u : 0u);
-                    umma_commit(&ctl.mma[c]);
+                    umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();
             }
             TC_STAMP(1);
             // work off the critical path while the MMA runs
-            flush_out();
-            if (t + 1 < n_chunks) load_v(t + 1, v_nxt);
-            uint32_t bpk[4];  // bf16x2 pairs of sigmoid(beta) for my 8 tokens (the record holds bf16-rounded values)
+            const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk);
+            unsigned short v_cur[kChunk];  // value column v of this chunk (zero past the sequence end)
             {
-                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta) + 2 * half;
-                const float4 b0 = bp[0], b1 = bp[1];
-                bpk[0] = pack_bf2(b0.x, b0.y); bpk[1] = pack_bf2(b0.z, b0.w);
-                bpk[2] = pack_bf2(b1.x, b1.y); bpk[3] = pack_bf2(b1.z, b1.w);
+                const unsigned short* vt = reinterpret_cast<const unsigned short*>(cs + kSmV + s * 4096) + v;
+#pragma unroll
+                for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
             }
-            if (!mbar_wait_bounded(&ctl.mma[c], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            const float e_mine = reinterpret_cast<const float*>(st + kTcEt)[v];  // gate decay of my state column
+            uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta) (the record holds bf16-rounded values)
+            {
+                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
+#pragma unroll
+                for (int i4 = 0; i4 < 4; ++i4) {
+                    const float4 b = bp[i4];
+                    bpk[2 * i4] = pack_bf2(b.x, b.y);
+                    bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
+                }
+            }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(2);
 
-            // ---- u' = (v (-) bf(u0)) (*) bf(beta) for my 8 tokens -> my half of the A operand ----
+            // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
             {
-                uint32_t r[8];
-                tmem_ld8(t_d1 + 8 * half + lane_sel, r);
+                uint32_t r[16];
+                tmem_ld16(t_d1 + lane_sel, r);
                 tmem_wait_ld();
-                uint32_t up[4];
+                uint32_t up[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < 8; ++i) {
                     const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
                     const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
                     up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
                 }
-                *reinterpret_cast<uint4*>(a23_mine) = make_uint4(up[0], up[1], up[2], up[3]);
+                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
+                *reinterpret_cast<uint4*>(ap) = make_uint4(up[0], up[1], up[2], up[3]);
+                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(up[4], up[5], up[6], up[7]);
             }
             TC_STAMP(3);
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_barrier_sync(bar_id, kTcChainThreads);
+            named_barrier_sync(bar_id, 128);
             TC_STAMP(4);
 
-            // ---- MMA2: D2[V,16] = u'^T . INV^T  (into the first 16 DS columns) ----
-            if (wic == 0) {
+            // ---- MMA2: D2[V,16] = u'^T . INV^T  (into the first 16 DST columns) ----
+            if (wiw == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
                     umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
-                    umma_commit(&ctl.mma[c]);
+                    umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&ctl.mma[c], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(5);
             {
-                uint32_t r[8];
-                tmem_ld8(t_ds + 8 * half + lane_sel, r);
+                uint32_t r[16];
+                tmem_ld16(t_ds + lane_sel, r);
                 tmem_wait_ld();
-                *reinterpret_cast<uint4*>(a23_mine) =
-                    make_uint4(pack_bf2(__uint_as_float(r[0]), __uint_as_float(r[1])),
-                               pack_bf2(__uint_as_float(r[2]), __uint_as_float(r[3])),
-                               pack_bf2(__uint_as_float(r[4]), __uint_as_float(r[5])),
-                               pack_bf2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
+                uint32_t p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
+                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
             }
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_barrier_sync(bar_id, kTcChainThreads);
+            named_barrier_sync(bar_id, 128);
             TC_STAMP(6);
 
-            // ---- MMA3: D3[V,16] = U^T . Mqk^T (over the dead u0 columns);  DS[V,K] = U^T . kr ----
-            if (wic == 0) {
+            // ---- MMA3: D3[V,16] = U^T . Mqk^T (over the dead u0 columns);  DST[K,V] = kr^T . U ----
+            if (wiw == 0) {
                 if (elect_one()) {
+                    bulk_wait_group_read<0>();  // the previous out tile has been read by its TMA store
                     tc_fence_after_sync();
                     umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
-                    umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcKr, 2048, 128), idesc_ds, 0u);
-                    umma_commit(&ctl.mma[c]);
+                    umma_ss(t_ds, make_smem_desc(st_addr + kTcKr, 2048, 128), a23_desc, idesc_dst, 0u);
+                    umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&ctl.mma[c], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(7);
 
-            // ---- my 64 state columns: S[v][k] = bf(fma(S[v][k], E_tot[k], DS[v][k])), TMEM loads one
-            //      batch of 16 columns ahead; out = bf(o0) (+) bf(Mqk U) for my 8 tokens is formed here and
-            //      stored while the next chunk's first MMA runs ----
-            auto update_cols = [&](int b, const uint32_t (&r)[16]) {
-                // all loads of the batch first: the stores below may alias them as far as the compiler knows
-                const int kc0 = 8 * half + 2 * b;
-                const float4* ep = reinterpret_cast<const float4*>(st + kTcEt) + 2 * kc0;
-                uint4 sv[2];
-                float4 e[4];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) sv[q] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, kc0 + q));
-#pragma unroll
-                for (int q = 0; q < 4; ++q) e[q] = ep[q];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const float4 e0 = e[2 * q], e1 = e[2 * q + 1];
-                    const uint32_t* rr = r + q * 8;
-                    uint4 nv;
-                    nv.x = pack_bf2(__fmaf_rn(bf_lo(sv[q].x), e0.x, __uint_as_float(rr[0])),
-                                    __fmaf_rn(bf_hi(sv[q].x), e0.y, __uint_as_float(rr[1])));
-                    nv.y = pack_bf2(__fmaf_rn(bf_lo(sv[q].y), e0.z, __uint_as_float(rr[2])),
-                                    __fmaf_rn(bf_hi(sv[q].y), e0.w, __uint_as_float(rr[3])));
-                    nv.z = pack_bf2(__fmaf_rn(bf_lo(sv[q].z), e1.x, __uint_as_float(rr[4])),
-                                    __fmaf_rn(bf_hi(sv[q].z), e1.y, __uint_as_float(rr[5])));
-                    nv.w = pack_bf2(__fmaf_rn(bf_lo(sv[q].w), e1.z, __uint_as_float(rr[6])),
-                                    __fmaf_rn(bf_hi(sv[q].w), e1.w, __uint_as_float(rr[7])));
-                    *reinterpret_cast<uint4*>(cs + kSmS + s_off(v, kc0 + q)) = nv;
-                }
-            };
+            // ---- out = bf(o0) (+) bf(Mqk U) (thread = V row), stored while the next chunk's MMA1 runs ----
             {
-                uint32_t ra[16], rb[16], r3[8], ro[8];
-                const uint32_t ds_mine = t_ds + 64 * half + lane_sel;
-                tmem_ld16(ds_mine, ra);
-                tmem_ld8(t_d1 + 8 * half + lane_sel, r3);
-                tmem_ld8(t_d1 + 16 + 8 * half + lane_sel, ro);
+                uint32_t r[32];
+                tmem_ld32(t_d1 + lane_sel, r);  // D3 in 0-15, o0 in 16-31
                 tmem_wait_ld();
-                tmem_ld16(ds_mine + 16, rb);
-                update_cols(0, ra);
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    o_pend[i] = bf2_add(pack_bf2(__uint_as_float(ro[2 * i]), __uint_as_float(ro[2 * i + 1])),
-                                        pack_bf2(__uint_as_float(r3[2 * i]), __uint_as_float(r3[2 * i + 1])));
-                o_pend_t = t;
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t o = bf2_add(pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1])),
+                                               pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+                    if (len == kChunk) {  // full chunk: through the out tile and one TMA store
+                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i) * kD + v] = (unsigned short)(o & 0xffffu);
+                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i + 1) * kD + v] = (unsigned short)(o >> 16);
+                    } else {              // ragged tail: only the valid rows, straight to global memory
+                        unsigned short* dst = ocol + ((int64_t)t * kChunk + 2 * i) * tstride;
+                        if (2 * i < len) dst[0] = (unsigned short)(o & 0xffffu);
+                        if (2 * i + 1 < len) dst[tstride] = (unsigned short)(o >> 16);
+                    }
+                }
+            }
+            // ---- state column k (thread = TMEM lane k of DST): S[vv][k] = bf(fma(S[vv][k], E_tot[k], DST[k][vv])),
+            //      registers only; the refreshed column also goes to the S^T tile for the next chunk's MMA1 ----
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                uint32_t r[32];
+                tmem_ld32(t_ds + 32 * b + lane_sel, r);
                 tmem_wait_ld();
-                tmem_ld16(ds_mine + 32, ra);
-                update_cols(1, rb);
-                tmem_wait_ld();
-                tmem_ld16(ds_mine + 48, rb);
-                update_cols(2, ra);
-                tmem_wait_ld();
-                update_cols(3, rb);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t sv = sreg[16 * b + i];
+                    sreg[16 * b + i] = pack_bf2(__fmaf_rn(bf_lo(sv), e_mine, __uint_as_float(r[2 * i])),
+                                                __fmaf_rn(bf_hi(sv), e_mine, __uint_as_float(r[2 * i + 1])));
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    *reinterpret_cast<uint4*>(cs + kSmS + sT_off(v, 4 * b + q)) =
+                        make_uint4(sreg[16 * b + 4 * q], sreg[16 * b + 4 * q + 1], sreg[16 * b + 4 * q + 2],
+                                   sreg[16 * b + 4 * q + 3]);
             }
             TC_STAMP(9);
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            named_barrier_sync(bar_id, kTcChainThreads);
+            named_barrier_sync(bar_id, 128);
             TC_STAMP(10);
 
-            // ---- refill the stage just consumed ----
-            if ((threadIdx.x & 255) == 0 && t + kTcStages < n_chunks) issue_load(t + kTcStages);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v_cur[i] = v_nxt[i];
+            // ---- store the out tile, refill the stage just consumed ----
+            if (wiw == 0) {
+                if (elect_one()) {
+                    if (len == kChunk) {
+                        tma_store_3d(&maps.out, 0, h, (int)(bos + (int64_t)t * kChunk), out_tile);
+                        bulk_commit_group();
+                    }
+                    if (t + kTcStages < n_chunks) issue_load(t + kTcStages);
+                }
+                __syncwarp();
+            }
             TC_STAMP(11);
 #ifdef FKDA_TC_TIMING
             if (stamp_on && t == 65) {
@@ -387,32 +373,34 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
 #endif
         }
         if (failed) break;
-        flush_out();
 
-        // ---- final state (my 64 columns): bf16, or the bf16 state widened to fp32 ----
+        // ---- final state: my column, bf16 or widened to fp32 ----
         if (a.final_state != nullptr) {
             if (a.state_fp32) {
-                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.final_state) + st_off);
-#pragma unroll 4
-                for (int q = 0; q < 8; ++q) {
-                    const uint4 sv = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, 8 * half + q));
-                    dst[2 * q] = make_float4(bf_lo(sv.x), bf_hi(sv.x), bf_lo(sv.y), bf_hi(sv.y));
-                    dst[2 * q + 1] = make_float4(bf_lo(sv.z), bf_hi(sv.z), bf_lo(sv.w), bf_hi(sv.w));
+                float* dst = reinterpret_cast<float*>(a.final_state) + st_base;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    dst[(2 * i) * kD] = bf_lo(sreg[i]);
+                    dst[(2 * i + 1) * kD] = bf_hi(sreg[i]);
                 }
             } else {
-                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.final_state) + st_off);
-#pragma unroll 4
-                for (int q = 0; q < 8; ++q) dst[q] = *reinterpret_cast<const uint4*>(cs + kSmS + s_off(v, 8 * half + q));
+                unsigned short* dst = reinterpret_cast<unsigned short*>(a.final_state) + st_base;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    dst[(2 * i) * kD] = (unsigned short)(sreg[i] & 0xffffu);
+                    dst[(2 * i + 1) * kD] = (unsigned short)(sreg[i] >> 16);
+                }
             }
         }
-        // all rows exported and all operand reads done before the next chain overwrites S / the stages
-        named_barrier_sync(bar_id, kTcChainThreads);
+        // all operand reads done before the next chain overwrites the S^T tile / the stages
+        named_barrier_sync(bar_id, 128);
     }
 
     if (failed) {
         ctl.abort_flag = 1;
         atomicExch(a.status, FKDA_ERR_DEVICE_STATUS);
     }
+    bulk_wait_group<0>();  // (the store-issuing lanes) out tiles fully written
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) {
@@ -425,6 +413,36 @@ __global__ void __launch_bounds__(kTcChains * kTcChainThreads, 1) recurrence_tc_
 size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
     return kWsHeaderBytes + ws_prefix_bytes(N) +
            (size_t)H * (size_t)ws_tiles_upper_bound(T_total, N) * (size_t)kTcRecord;
+}
+
+// [token][head][128] bf16 view of a token-major tensor, boxes of 16 tokens x 1 head x 128 elements
+// The driver entry point is looked up through the runtime (no link-time dependency on libcuda, so
+// the library also loads on a machine without a driver).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+static bool encode_token_map(CUtensorMap* m, const void* base, int64_t T_total, int64_t H, int64_t token_stride) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)H, (cuuint64_t)(T_total > 0 ? T_total : 1)};
+    const cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)token_stride * 2};  // bytes, dims 1 and 2
+    const cuuint32_t box[3] = {(cuuint32_t)kD, 1u, (cuuint32_t)kChunk};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
@@ -456,7 +474,11 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         int64_t ctas = (chains + kTcChains - 1) / kTcChains;
         if (ctas > sms) ctas = sms;
         if (ctas < 1) ctas = 1;
-        recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * kTcChainThreads, kTcSmemBytes, stream>>>(a);
+        TcMaps maps;
+        if (!encode_token_map(&maps.v, p.v, p.B * p.T, p.H, p.token_stride) ||
+            !encode_token_map(&maps.out, p.out, p.B * p.T, p.H, p.token_stride))
+            return FKDA_ERR_LAUNCH;
+        recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a, maps);
         ++launches;
     }
     if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
