@@ -93,9 +93,12 @@ __global__ void __launch_bounds__(256) prepare_kernel(TwoPassArgs a) {
     }
     const float qinv = rsqrt_approx(__fadd_rn(qs, 1e-6f));
     const float kinv = rsqrt_approx(__fadd_rn(ks, 1e-6f));
-    __nv_bfloat16 qn[8], kn[8];
+    uint32_t qn[4], kn[4];  // normalised q, k as bf16x2 pairs
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { qn[i] = f2bf(__fmul_rn(qv[i], qinv)); kn[i] = f2bf(__fmul_rn(kv[i], kinv)); }
+    for (int i = 0; i < 4; ++i) {
+        qn[i] = pack_bf2(__fmul_rn(qv[2 * i], qinv), __fmul_rn(qv[2 * i + 1], qinv));
+        kn[i] = pack_bf2(__fmul_rn(kv[2 * i], kinv), __fmul_rn(kv[2 * i + 1], kinv));
+    }
 
     // ---- gate activation: gate_scale * sigmoid(exp(A_log) * (g + dt_bias)); 0 past the end ----
     const float a_exp = ex2_approx(__fmul_rn(a.A_log[h], 1.4426950408889634f));
@@ -103,11 +106,14 @@ __global__ void __launch_bounds__(256) prepare_kernel(TwoPassArgs a) {
         const float4 dt0 = *reinterpret_cast<const float4*>(a.dt_bias + (int64_t)h * kD + c8);
         const float4 dt1 = *reinterpret_cast<const float4*>(a.dt_bias + (int64_t)h * kD + c8 + 4);
         const float dt[8] = {dt0.x, dt0.y, dt0.z, dt0.w, dt1.x, dt1.y, dt1.z, dt1.w};
+        float gt[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float x = __fmul_rn(a_exp, __fadd_rn(gv[i], dt[i]));
-            sm.G[row][c8 + i] = valid ? __fmul_rn(a.gate_scale, sigmoid_tanh(x)) : 0.0f;
+            gt[i] = valid ? __fmul_rn(a.gate_scale, sigmoid_tanh(x)) : 0.0f;
         }
+        *reinterpret_cast<float4*>(&sm.G[row][c8]) = make_float4(gt[0], gt[1], gt[2], gt[3]);
+        *reinterpret_cast<float4*>(&sm.G[row][c8 + 4]) = make_float4(gt[4], gt[5], gt[6], gt[7]);
     }
     if (tid < kChunk) {
         float b = 0.0f;
@@ -128,30 +134,23 @@ __global__ void __launch_bounds__(256) prepare_kernel(TwoPassArgs a) {
     const int64_t rec = ((int64_t)h * a.total_tiles + tile) * (int64_t)(kTc ? kTcRecord : kWsRecord);
     uint8_t* ws = a.workspace + rec;
     {
-        const __nv_bfloat16 sc = f2bf(a.scale);
+        const uint32_t sc2 = pack_bf2(a.scale, a.scale);
+        const float4 g0 = *reinterpret_cast<const float4*>(&sm.G[row][c8]);
+        const float4 g1 = *reinterpret_cast<const float4*>(&sm.G[row][c8 + 4]);
+        const float4 t0v = *reinterpret_cast<const float4*>(&sm.etot[c8]);
+        const float4 t1v = *reinterpret_cast<const float4*>(&sm.etot[c8 + 4]);
+        const float G[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float Et[8] = {t0v.x, t0v.y, t0v.z, t0v.w, t1v.x, t1v.y, t1v.z, t1v.w};
         uint32_t kd_p[4], qd_p[4], ki_p[4], kr_p[4];
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-            __nv_bfloat16 r[4][2];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float G = sm.G[row][c8 + i + j];
-                const __nv_bfloat16 ep = f2bf(ex2_approx(G));
-                const __nv_bfloat16 em = f2bf(ex2_approx(-G));
-                const __nv_bfloat16 et = f2bf(sm.etot[c8 + i + j]);
-                r[0][j] = bfmul(kn[i + j], ep);
-                r[1][j] = bfmul(bfmul(qn[i + j], ep), sc);
-                r[2][j] = bfmul(kn[i + j], em);
-                r[3][j] = bfmul(r[2][j], et);
-            }
-            auto pk = [](__nv_bfloat16 lo, __nv_bfloat16 hi) {
-                __nv_bfloat162 v(lo, hi);
-                return *reinterpret_cast<uint32_t*>(&v);
-            };
-            kd_p[i / 2] = pk(r[0][0], r[0][1]);
-            qd_p[i / 2] = pk(r[1][0], r[1][1]);
-            ki_p[i / 2] = pk(r[2][0], r[2][1]);
-            kr_p[i / 2] = pk(r[3][0], r[3][1]);
+        for (int i = 0; i < 4; ++i) {  // bf16x2 arithmetic: one rounding per element and operation
+            const uint32_t ep = pack_bf2(ex2_approx(G[2 * i]), ex2_approx(G[2 * i + 1]));
+            const uint32_t em = pack_bf2(ex2_approx(-G[2 * i]), ex2_approx(-G[2 * i + 1]));
+            const uint32_t et = pack_bf2(Et[2 * i], Et[2 * i + 1]);
+            kd_p[i] = bf2_mul(kn[i], ep);
+            qd_p[i] = bf2_mul(bf2_mul(qn[i], ep), sc2);
+            ki_p[i] = bf2_mul(kn[i], em);
+            kr_p[i] = bf2_mul(ki_p[i], et);
         }
         const uint4 kd4 = make_uint4(kd_p[0], kd_p[1], kd_p[2], kd_p[3]);
         const uint4 qd4 = make_uint4(qd_p[0], qd_p[1], qd_p[2], qd_p[3]);
@@ -176,34 +175,49 @@ __global__ void __launch_bounds__(256) prepare_kernel(TwoPassArgs a) {
     if (kTc && tid < kChunk) reinterpret_cast<float*>(ws + kTcBeta)[tid] = bf2f(f2bf(sm.beta_act[tid]));
     __syncthreads();
 
-    // ---- L = fp16(kd ki^T) masked * fp16(beta), Mqk = bf16(qd ki^T) masked; thread (i, j) ----
-    {
-        const int i = tid >> 4, j = tid & 15;
-        float sl = 0.f, sq = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < kD; c += 8) {
-            const uint4 A = *reinterpret_cast<const uint4*>(&sm.kd[i][c]);
-            const uint4 Q = *reinterpret_cast<const uint4*>(&sm.qd[i][c]);
-            const uint4 Bv = *reinterpret_cast<const uint4*>(&sm.ki[j][c]);
-            const uint32_t* ap = &A.x; const uint32_t* qp = &Q.x; const uint32_t* bp = &Bv.x;
+    // ---- L = fp16(kd ki^T) masked * fp16(beta) (warp 0), Mqk = bf16(qd ki^T) masked (warp 1):
+    //      mma.sync m16n8k16 bf16 -> fp32, operand fragments fetched with conflict-free 32-bit loads ----
+    if (tid < 64) {
+        const int w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+        const __nv_bfloat16(*A)[kPitch] = (w == 0) ? sm.kd : sm.qd;
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                sl = __fmaf_rn(bf_lo(ap[e]), bf_lo(bp[e]), sl);
-                sq = __fmaf_rn(bf_lo(qp[e]), bf_lo(bp[e]), sq);
-                sl = __fmaf_rn(bf_hi(ap[e]), bf_hi(bp[e]), sl);
-                sq = __fmaf_rn(bf_hi(qp[e]), bf_hi(bp[e]), sq);
+        for (int j = 0; j < kD / 16; ++j) {
+            const int col = 16 * j + 2 * t;
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&A[g][col]);
+            const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&A[g + 8][col]);
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&A[g][col + 8]);
+            const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&A[g + 8][col + 8]);
+            const uint32_t b00 = *reinterpret_cast<const uint32_t*>(&sm.ki[g][col]);
+            const uint32_t b01 = *reinterpret_cast<const uint32_t*>(&sm.ki[g][col + 8]);
+            const uint32_t b10 = *reinterpret_cast<const uint32_t*>(&sm.ki[g + 8][col]);
+            const uint32_t b11 = *reinterpret_cast<const uint32_t*>(&sm.ki[g + 8][col + 8]);
+            mma_bf16_f32acc(c0, a0, a1, a2, a3, b00, b01);  // columns 0-7
+            mma_bf16_f32acc(c1, a0, a1, a2, a3, b10, b11);  // columns 8-15
+        }
+        // fragment element e of n-tile nt: row = g + 8*(e>>1), column = 8*nt + 2*t + (e&1)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                const int i = g + 8 * hr, j = 8 * nt + 2 * t;
+                const float x0 = nt ? c1[2 * hr] : c0[2 * hr], x1 = nt ? c1[2 * hr + 1] : c0[2 * hr + 1];
+                if (w == 0) {
+                    const __half bh = __float2half_rn(sm.beta_act[i]);
+                    const __half l0 = (i > j) ? __hmul(__float2half_rn(x0), bh) : __float2half_rn(0.0f);
+                    const __half l1 = (i > j + 1) ? __hmul(__float2half_rn(x1), bh) : __float2half_rn(0.0f);
+                    *reinterpret_cast<__half2*>(&sm.L[i][j]) = __halves2half2(l0, l1);
+                } else {
+                    const uint32_t m = pack_bf2((i >= j) ? x0 : 0.0f, (i >= j + 1) ? x1 : 0.0f);
+                    if constexpr (kTc)
+                        *reinterpret_cast<uint32_t*>(ws + kTcMqk + tc_sq_off(i, j)) = m;
+                    else
+                        *reinterpret_cast<uint32_t*>(ws + kWsMqk + (i * kChunk + j) * 2) = m;
+                }
             }
         }
-        __half l = __float2half_rn(0.0f);
-        if (i > j) l = __hmul(__float2half_rn(sl), __float2half_rn(sm.beta_act[i]));
-        sm.L[i][j] = l;
-        const __nv_bfloat16 mq = (i >= j) ? f2bf(sq) : f2bf(0.0f);
-        if constexpr (kTc)
-            *reinterpret_cast<__nv_bfloat16*>(ws + kTcMqk + tc_sq_off(i, j)) = mq;
-        else
-            reinterpret_cast<__nv_bfloat16*>(ws + kWsMqk)[i * kChunk + j] = mq;
     }
-    __syncthreads();
+    __syncwarp();
     if (tid < 32)
         neumann_inverse_warp<kTc>(&sm.L[0][0], &sm.W[0][0], kLd16, ws + (kTc ? kTcInv : kWsInv), tid);
 }
