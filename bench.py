@@ -235,7 +235,7 @@ def run_ours(a):
     value = world * w.tokens / (ms_step * 1e-3)
 
     # ---- dominant kernel alone (CUDA events on the launching stream) ----
-    kernel_name = {"tc": "fkda::recurrence_tc_kernel"}.get(algo, "fkda::recurrence_kernel")
+    kernel_name = {"twopass": "fkda::recurrence_kernel"}.get(algo, "fkda::recurrence_tc_kernel")
     kernel_ms = None
     n_phase = 3
     barrier()

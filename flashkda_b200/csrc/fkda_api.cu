@@ -31,7 +31,7 @@ const char* fkda_status_string(int status) {
 }
 
 static int resolve_algo(int32_t algo) {
-    if (algo == FKDA_ALGO_AUTO) return FKDA_ALGO_TWOPASS;
+    if (algo == FKDA_ALGO_AUTO) return FKDA_ALGO_TC;
     return algo;
 }
 

@@ -20,8 +20,12 @@ struct TwoPassArgs {
     const int64_t* cu_seqlens;
     int32_t* tile_prefix;  // [N + 1] chunk-count prefix (varlen only)
     uint8_t* workspace;    // [H][total_tiles] per-chunk records
-    int32_t* queue;        // work-queue counter of the persistent recurrence (zeroed per call)
-    int32_t* status;       // device status word: 0 ok, else the code of a bounded wait that gave up
+    int32_t* queue;        // header word 0: ticket counter of the persistent recurrence (zeroed per call)
+    int32_t* status;       // header word 1: device status, 0 ok, else the code of a bounded wait that gave up
+                           // (header words 2, 3: push counter and finished-chain counter of the segment queue)
+    int32_t* qslots;       // segment queue: slot i receives the i-th pushed item (-1 = not yet pushed)
+    uint32_t* seg_state;   // [chain][16][128] uint4: bf16 state handed from one segment of a chain to the next
+    int32_t seg_chunks;    // chunks per scheduling segment (0 = whole chains)
     int64_t T, H, N, total_tiles;
     int64_t token_stride, beta_token_stride;
     float scale, gate_scale;
@@ -29,7 +33,7 @@ struct TwoPassArgs {
 };
 
 // Workspace layout of both two-pass implementations:
-//   [0, 256)  header: int32 queue counter, int32 device status
+//   [0, 256)  header: int32 ticket counter, device status, push counter, finished-chain counter
 //   [256, ..) tile prefix (N + 1 int32, padded to 256 B)
 //   then      H * total_tiles records
 constexpr size_t kWsHeaderBytes = 256;

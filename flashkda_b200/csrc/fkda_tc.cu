@@ -129,11 +129,38 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 #endif
 
     while (!failed) {
-        // ---- next chain from the work queue ----
-        if (v == 0) ctl.next_chain[wg] = atomicAdd(a.queue, 1);
+        // ---- next work item.  An item is one segment (seg_chunks chunks) of one chain; item id =
+        //      seg * n_chains + chain.  Tickets below n_chains are the first segments; every later ticket
+        //      reads the slot that the finisher of some segment fills with the follow-up segment, so chains
+        //      take turns on the chain slots (first come, first served) and more chains than slots still
+        //      share the machine evenly.  A waiter leaves when all chains are finished. ----
+        if (v == 0) {
+            const int ticket = atomicAdd(a.queue, 1);
+            int item = -2;  // -2: no more work, -3: gave up waiting
+            if (ticket < n_chains) {
+                item = ticket;
+            } else if (a.seg_chunks > 0) {
+                volatile int32_t* slot = a.qslots + (ticket - (int)n_chains);
+                volatile int32_t* finished = a.queue + 3;
+                const uint64_t t0 = global_timer_ns();
+                uint32_t spins = 0;
+                for (;;) {
+                    const int x = *slot;
+                    if (x >= 0) { item = x; break; }
+                    if (*finished >= (int)n_chains) break;
+                    if ((++spins & 63u) == 0 && (*abort_flag != 0 || global_timer_ns() - t0 > kTcWaitNs)) { item = -3; break; }
+                    __nanosleep(200);
+                }
+                __threadfence();  // the pusher's state stores are visible before we read them
+            }
+            ctl.next_chain[wg] = item;
+        }
         named_barrier_sync(bar_id, 128);
-        const int64_t chain = ctl.next_chain[wg];
-        if (chain >= n_chains) break;
+        const int item = ctl.next_chain[wg];
+        if (item == -3) { failed = true; break; }
+        if (item < 0) break;
+        const int seg = item / (int)n_chains;
+        const int64_t chain = item - (int64_t)seg * n_chains;
         const int64_t n = chain / a.H;
         const int h = (int)(chain - n * a.H);
         int64_t bos, seq_len, tile_base;
@@ -148,6 +175,8 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             tile_base = n * ((a.T + kChunk - 1) / kChunk);
         }
         const int n_chunks = (int)((seq_len + kChunk - 1) / kChunk);
+        const int c0 = seg * a.seg_chunks;                                             // my chunk range
+        const int c1 = (a.seg_chunks > 0 && c0 + a.seg_chunks < n_chunks) ? c0 + a.seg_chunks : n_chunks;
         const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
         // thread k = v owns state column k: element S[vv][k] of this chain sits at st_base + vv * 128
         const int64_t st_base = (n * a.H + h) * (int64_t)(kD * kD) + v;
@@ -163,14 +192,21 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             tma_load_3d(cs + kSmV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[wg][s]);
         };
         if (v == 0) {
-            for (int t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
+            for (int t = c0; t < c0 + kTcStages && t < c1; ++t) issue_load(t);
         }
         const int64_t tstride = a.token_stride;
         unsigned short* ocol = reinterpret_cast<unsigned short*>(a.out) + bos * tstride + (int64_t)h * kD + v;
 
         // ---- initial state: column k of S into registers (pairs over v) and into the S^T tile ----
         uint32_t sreg[64];
-        if (a.initial_state != nullptr) {
+        uint4* const seg_mine = reinterpret_cast<uint4*>(a.seg_state) + (chain * 16) * 128 + v;  // + i * 128
+        if (seg > 0) {  // handed over by the previous segment (another SM wrote it: bypass L1)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint4 x = __ldcg(seg_mine + i * 128);
+                sreg[4 * i] = x.x; sreg[4 * i + 1] = x.y; sreg[4 * i + 2] = x.z; sreg[4 * i + 3] = x.w;
+            }
+        } else if (a.initial_state != nullptr) {
             if (a.state_fp32) {
                 const float* src = reinterpret_cast<const float*>(a.initial_state) + st_base;
 #pragma unroll
@@ -194,7 +230,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 
         __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kSmOut);
 
-        for (int t = 0; t < n_chunks; ++t) {
+        for (int t = c0; t < c1; ++t) {
             const int s = t % kTcStages;
             uint8_t* st = cs + kSmStage + s * kSmStageBytes;
             const uint32_t st_addr = smem_u32(st);
@@ -360,7 +396,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
                         tma_store_3d(&maps.out, 0, h, (int)(bos + (int64_t)t * kChunk), out_tile);
                         bulk_commit_group();
                     }
-                    if (t + kTcStages < n_chunks) issue_load(t + kTcStages);
+                    if (t + kTcStages < c1) issue_load(t + kTcStages);
                 }
                 __syncwarp();
             }
@@ -374,6 +410,21 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
         }
         if (failed) break;
 
+        if (c1 < n_chunks) {
+            // ---- not the last segment: hand the state over and queue the follow-up segment ----
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                seg_mine[i * 128] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
+            __threadfence();
+            named_barrier_sync(bar_id, 128);
+            if (v == 0) {
+                const int pos = atomicAdd(a.queue + 2, 1);
+                __threadfence();
+                *reinterpret_cast<volatile int32_t*>(a.qslots + pos) = item + (int)n_chains;
+            }
+            continue;
+        }
+        if (v == 0) atomicAdd(a.queue + 3, 1);  // this chain is finished
         // ---- final state: my column, bf16 or widened to fp32 ----
         if (a.final_state != nullptr) {
             if (a.state_fp32) {
@@ -410,12 +461,25 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------
+// Segment scheduling is used when there are more chains than a B200 can hold at once (3 per SM);
+// with fewer chains every chain has its own slot and whole chains are the work items.
+constexpr int64_t kSegThresholdChains = 384;
+constexpr int kSegChunks = 64;  // even, so that the double-buffer parity of a segment's first chunk is fixed
+static bool use_segments(int64_t H, int64_t N) { return H * N > kSegThresholdChains; }
+static size_t seg_slot_count(int64_t T_total, int64_t H, int64_t N) {
+    // one push per segment after the first of each chain, plus one ticket per resident warpgroup at the end
+    return (size_t)(H * (ws_tiles_upper_bound(T_total, N) / kSegChunks + N) + 4096);
+}
+static size_t seg_slots_bytes(int64_t T_total, int64_t H, int64_t N) {
+    return use_segments(H, N) ? (seg_slot_count(T_total, H, N) * 4 + 255) / 256 * 256 : 0;
+}
+static size_t seg_state_bytes(int64_t H, int64_t N) { return use_segments(H, N) ? (size_t)(H * N) * 32768 : 0; }
+
 size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
-    return kWsHeaderBytes + ws_prefix_bytes(N) +
+    return kWsHeaderBytes + ws_prefix_bytes(N) + seg_slots_bytes(T_total, H, N) + seg_state_bytes(H, N) +
            (size_t)H * (size_t)ws_tiles_upper_bound(T_total, N) * (size_t)kTcRecord;
 }
 
-// [token][head][128] bf16 view of a token-major tensor, boxes of 16 tokens x 1 head x 128 elements
 // The driver entry point is looked up through the runtime (no link-time dependency on libcuda, so
 // the library also loads on a machine without a driver).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -452,7 +516,19 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     const bool do_prep = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_PREPARE);
     const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
     int launches = 0;
-    if (cudaMemsetAsync(p.workspace, 0, 8, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;  // queue + status
+    if (cudaMemsetAsync(p.workspace, 0, 16, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;  // header counters
+    {   // carve the segment queue and the hand-over states in front of the records
+        const int64_t T_total = p.B * p.T;
+        uint8_t* base = reinterpret_cast<uint8_t*>(p.workspace) + kWsHeaderBytes + ws_prefix_bytes(p.N);
+        const size_t slots = seg_slots_bytes(T_total, p.H, p.N), states = seg_state_bytes(p.H, p.N);
+        if (use_segments(p.H, p.N)) {
+            a.qslots = reinterpret_cast<int32_t*>(base);
+            a.seg_state = reinterpret_cast<uint32_t*>(base + slots);
+            a.seg_chunks = kSegChunks;
+            if (do_rec && cudaMemsetAsync(a.qslots, 0xff, slots, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;
+        }
+        a.workspace = base + slots + states;
+    }
     if (varlen && do_prep) {
         launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, stream);
         ++launches;

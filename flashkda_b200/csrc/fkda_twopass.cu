@@ -237,6 +237,9 @@ void fill_args(const fkda_fwd_params& p, TwoPassArgs* out) {
     uint8_t* base = reinterpret_cast<uint8_t*>(p.workspace);
     a.queue = reinterpret_cast<int32_t*>(base);
     a.status = reinterpret_cast<int32_t*>(base) + 1;
+    a.qslots = nullptr;
+    a.seg_state = nullptr;
+    a.seg_chunks = 0;
     a.tile_prefix = reinterpret_cast<int32_t*>(base + kWsHeaderBytes);
     a.workspace = base + kWsHeaderBytes + ws_prefix_bytes(p.N);
 }
@@ -246,7 +249,7 @@ int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launche
     fill_args(p, &a);
     const bool varlen = p.cu_seqlens != nullptr;
     int launches = 0;
-    if (cudaMemsetAsync(p.workspace, 0, 8, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;  // queue + status
+    if (cudaMemsetAsync(p.workspace, 0, 16, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;  // queue + status
     const bool do_prep = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_PREPARE);
     const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
     if (varlen && do_prep) {

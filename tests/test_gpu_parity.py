@@ -234,3 +234,36 @@ def test_tensor_core_path_matches_cuda_core_path():
     assert oracle.err_ratio(o1, o2) <= 2e-3
     assert oracle.err_ratio(h1, h2) <= 1e-3
     assert mism <= 0.05
+
+
+def test_segment_scheduling_many_chains():
+    """More chains than the GPU holds at once (> 384): the tensor-core path then schedules 64-chunk
+    segments and hands the state from one segment to the next through the workspace.  Long and short
+    sequences mixed, so that chains span one to three segments."""
+    gen = torch.Generator().manual_seed(5)
+    lens = torch.randint(1, 2500, (100,), generator=gen).tolist()
+    lens[7], lens[50], lens[99] = 1, 1024, 3000
+    w = Workload("seg", 1, sum(lens), 4, state_in="bf16", state_out="bf16", seq_lens=lens)
+    inp = make_inputs(w, seed=12)
+    ref_out, ref_hT = run_oracle(inp)
+    out, hT = run_gpu(inp, "tc")
+    check_against(out, hT, ref_out, ref_hT)
+    out2, hT2 = run_gpu(inp, "twopass")
+    assert oracle.err_ratio(out2, out) <= 2e-3
+    assert oracle.err_ratio(hT2, hT) <= 1e-3
+
+
+def test_segment_scheduling_fixed_batch():
+    w = Workload("segf", 50, 1200, 8, state_in="fp32", state_out="fp32")
+    inp = make_inputs(w, seed=13)
+    out, hT = run_gpu(inp, "tc")
+    out2, hT2 = run_gpu(inp, "twopass")
+    assert oracle.err_ratio(out2, out) <= 2e-3
+    assert oracle.err_ratio(hT2, hT) <= 1e-3
+    # a few sequences against the oracle (the whole batch would take the CPU a while)
+    sub = dict(inp)
+    for key in ("q", "k", "v", "g", "beta", "initial_state"):
+        sub[key] = inp[key][:3].contiguous()
+    sub["final_state"] = torch.zeros_like(sub["initial_state"])
+    ref_out, ref_hT = run_oracle(sub)
+    check_against(out[:3], hT[:3], ref_out, ref_hT)
