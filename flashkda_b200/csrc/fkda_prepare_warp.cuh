@@ -1,0 +1,264 @@
+// Warp-per-chunk "prepare" stage: one warp turns one (chunk, head) of q, k, g, beta into the chunk
+// operands kd, qd, kr, E_tot, INV, Mqk (workspace record), with no block-level synchronisation:
+// lane l owns columns 4l..4l+3 of all 16 token rows, so the in-chunk gate cumsum runs in registers,
+// the q/k row norms use warp shuffles (in the exact summation order of the contract: an FMA chain
+// over each group of 8 columns, then a butterfly over the 16 groups), and only the two small
+// 16x16x128 products (mma.sync bf16) and the 16x16 inverse (mma.sync f16) go through a few KB of
+// per-warp shared memory.  Warps are independent, so the same routine serves as a producer inside
+// a persistent kernel.  Numerics: tests/torch_ref.py:153-229 of the reference.
+#pragma once
+
+#include "fkda_common.cuh"
+#include "fkda_internal.h"
+
+namespace fkda {
+
+constexpr int kPwPitch = kD + 8;  // bf16 row pitch (272 B): conflict-free fragment loads
+constexpr int kPwLd16 = 24;       // fp16 row pitch of the 16x16 matrices
+
+struct PrepWarpSmem {
+    __nv_bfloat16 kd[kChunk][kPwPitch];  // k * 2^G
+    __nv_bfloat16 qd[kChunk][kPwPitch];  // q * 2^G * scale
+    __nv_bfloat16 ki[kChunk][kPwPitch];  // k * 2^-G
+    __half L[kChunk][kPwLd16];
+    __half W[kChunk][kPwLd16];
+    float beta_act[kChunk];
+};
+
+// Where chunk `tile` of the (possibly ragged) batch lives: first token and number of valid rows.
+// Returns false for a tile index past the last chunk (ragged upper bound).
+__device__ __forceinline__ bool locate_tile(const TwoPassArgs& a, int64_t tile, int64_t* t0, int* len) {
+    int64_t n, local_t, bos, seq_len;
+    if (a.cu_seqlens != nullptr) {
+        const int32_t* pre = a.tile_prefix;
+        if (tile >= pre[a.N]) return false;
+        int64_t lo = 0, hi = a.N;  // find n with pre[n] <= tile < pre[n+1]
+        while (hi - lo > 1) {
+            int64_t mid = (lo + hi) >> 1;
+            if (pre[mid] <= tile) lo = mid; else hi = mid;
+        }
+        n = lo;
+        local_t = tile - pre[n];
+        bos = a.cu_seqlens[n];
+        seq_len = a.cu_seqlens[n + 1] - bos;
+    } else {
+        const int64_t tps = (a.T + kChunk - 1) / kChunk;
+        n = tile / tps;
+        local_t = tile - n * tps;
+        bos = n * a.T;
+        seq_len = a.T;
+    }
+    *t0 = bos + local_t * kChunk;
+    *len = (int)min((int64_t)kChunk, seq_len - local_t * kChunk);
+    return true;
+}
+
+// Sum of squares of one 128-wide row held 4 columns per lane, in the contract's order: FMA chain
+// over columns 8m..8m+7 (lanes 2m then 2m+1), then xor-butterfly with offsets 8,4,2,1 over the 16
+// groups.  All lanes return the row total.
+__device__ __forceinline__ float row_sumsq(const float (&x)[4], int lane) {
+    float p = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p = __fmaf_rn(x[i], x[i], p);
+    const float first = __shfl_sync(0xffffffffu, p, lane & ~1);  // partial of the even lane of my pair
+    float c = first;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c = __fmaf_rn(x[i], x[i], c);     // odd lanes: chain continued over their 4
+#pragma unroll
+    for (int off = 16; off >= 2; off >>= 1) c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, off));
+    return __shfl_sync(0xffffffffu, c, lane | 1);                 // the odd lanes hold the group sums
+}
+
+// One warp, one (chunk, head).  `ws` is the record to fill; kTc selects its layout (see fkda_common.cuh).
+template <bool kTc>
+__device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t t0, int len, int h, uint8_t* ws,
+                                                   PrepWarpSmem& sm, int lane) {
+    const int c4 = lane * 4;  // my 4 columns
+    const float a_exp = ex2_approx(__fmul_rn(a.A_log[h], 1.4426950408889634f));
+    const float4 dtv = *reinterpret_cast<const float4*>(a.dt_bias + (int64_t)h * kD + c4);
+    const float dt[4] = {dtv.x, dtv.y, dtv.z, dtv.w};
+    const uint32_t sc2 = pack_bf2(a.scale, a.scale);
+    const __nv_bfloat16* qp = a.q + t0 * a.token_stride + (int64_t)h * kD + c4;
+    const __nv_bfloat16* kp = a.k + t0 * a.token_stride + (int64_t)h * kD + c4;
+    const __nv_bfloat16* gp = a.g + t0 * a.token_stride + (int64_t)h * kD + c4;
+
+    // sigmoid(beta) of row `lane` (rows past the end use logit 0, as zero padding does)
+    if (lane < kChunk) {
+        float b = 0.0f;
+        if (lane < len) b = bf2f(a.beta[(t0 + lane) * a.beta_token_stride + h]);
+        const float sb = sigmoid_tanh(b);
+        sm.beta_act[lane] = sb;
+        if constexpr (kTc) reinterpret_cast<float*>(ws + kTcBeta)[lane] = bf2f(f2bf(sb));
+    }
+
+    float csum[4] = {0.f, 0.f, 0.f, 0.f};  // running in-chunk gate sum of my columns
+    // rows are fetched kPf rows ahead of their use so that several DRAM round trips overlap
+    constexpr int kPf = 4;
+    uint2 ring_q[kPf], ring_k[kPf], ring_g[kPf];
+    auto fetch = [&](int r, int slot) {
+        ring_q[slot] = ring_k[slot] = ring_g[slot] = make_uint2(0, 0);
+        if (r < len) {
+            ring_q[slot] = __ldg(reinterpret_cast<const uint2*>(qp + (int64_t)r * a.token_stride));
+            ring_k[slot] = __ldg(reinterpret_cast<const uint2*>(kp + (int64_t)r * a.token_stride));
+            ring_g[slot] = __ldg(reinterpret_cast<const uint2*>(gp + (int64_t)r * a.token_stride));
+        }
+    };
+#pragma unroll
+    for (int r = 0; r < kPf; ++r) fetch(r, r);
+#pragma unroll 1
+    for (int rb = 0; rb < kChunk; rb += kPf) {
+#pragma unroll
+    for (int rr = 0; rr < kPf; ++rr) {
+        const int r = rb + rr;
+        const bool valid = r < len;
+        const uint2 qraw = ring_q[rr], kraw = ring_k[rr], graw = ring_g[rr];
+        if (r + kPf < kChunk) fetch(r + kPf, rr);
+        const float qv[4] = {bf_lo(qraw.x), bf_hi(qraw.x), bf_lo(qraw.y), bf_hi(qraw.y)};
+        const float kv[4] = {bf_lo(kraw.x), bf_hi(kraw.x), bf_lo(kraw.y), bf_hi(kraw.y)};
+        const float gv[4] = {bf_lo(graw.x), bf_hi(graw.x), bf_lo(graw.y), bf_hi(graw.y)};
+        // q/k L2 normalisation
+        const float qinv = rsqrt_approx(__fadd_rn(row_sumsq(qv, lane), 1e-6f));
+        const float kinv = rsqrt_approx(__fadd_rn(row_sumsq(kv, lane), 1e-6f));
+        const uint32_t qn0 = pack_bf2(__fmul_rn(qv[0], qinv), __fmul_rn(qv[1], qinv));
+        const uint32_t qn1 = pack_bf2(__fmul_rn(qv[2], qinv), __fmul_rn(qv[3], qinv));
+        const uint32_t kn0 = pack_bf2(__fmul_rn(kv[0], kinv), __fmul_rn(kv[1], kinv));
+        const uint32_t kn1 = pack_bf2(__fmul_rn(kv[2], kinv), __fmul_rn(kv[3], kinv));
+        // gate = gate_scale * sigmoid(exp(A_log) * (g + dt_bias)), 0 past the end; cumulative over rows
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float x = __fmul_rn(a_exp, __fadd_rn(gv[i], dt[i]));
+            const float gt = valid ? __fmul_rn(a.gate_scale, sigmoid_tanh(x)) : 0.0f;
+            csum[i] = __fadd_rn(csum[i], gt);
+        }
+        // decay application in bf16x2: one rounding per element and operation
+        const uint32_t ep0 = pack_bf2(ex2_approx(csum[0]), ex2_approx(csum[1]));
+        const uint32_t ep1 = pack_bf2(ex2_approx(csum[2]), ex2_approx(csum[3]));
+        const uint32_t em0 = pack_bf2(ex2_approx(-csum[0]), ex2_approx(-csum[1]));
+        const uint32_t em1 = pack_bf2(ex2_approx(-csum[2]), ex2_approx(-csum[3]));
+        const uint2 kd = make_uint2(bf2_mul(kn0, ep0), bf2_mul(kn1, ep1));
+        const uint2 qd = make_uint2(bf2_mul(bf2_mul(qn0, ep0), sc2), bf2_mul(bf2_mul(qn1, ep1), sc2));
+        *reinterpret_cast<uint2*>(&sm.kd[r][c4]) = kd;
+        *reinterpret_cast<uint2*>(&sm.qd[r][c4]) = qd;
+        *reinterpret_cast<uint2*>(&sm.ki[r][c4]) = make_uint2(bf2_mul(kn0, em0), bf2_mul(kn1, em1));
+        if constexpr (kTc) {
+            const int off = tc_b1_off(r, lane >> 1) + (lane & 1) * 8;
+            *reinterpret_cast<uint2*>(ws + kTcB1 + off) = kd;
+            *reinterpret_cast<uint2*>(ws + kTcB1 + off + 2 * 128) = qd;  // rows 16..31 = two row groups further
+        } else {
+            *reinterpret_cast<uint2*>(ws + kWsKd + (r * kD + c4) * 2) = kd;
+            *reinterpret_cast<uint2*>(ws + kWsQd + (r * kD + c4) * 2) = qd;
+        }
+    }
+    }
+    // E_tot and kr (ki read back from my own columns of the tile)
+    {
+        float et[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) et[i] = ex2_approx(csum[i]);
+        *reinterpret_cast<float4*>(ws + (kTc ? kTcEt : kWsEt) + c4 * 4) = make_float4(et[0], et[1], et[2], et[3]);
+        const uint32_t et0 = pack_bf2(et[0], et[1]), et1 = pack_bf2(et[2], et[3]);
+#pragma unroll
+        for (int r = 0; r < kChunk; ++r) {
+            const uint2 ki = *reinterpret_cast<const uint2*>(&sm.ki[r][c4]);
+            const uint2 kr = make_uint2(bf2_mul(ki.x, et0), bf2_mul(ki.y, et1));
+            if constexpr (kTc)
+                *reinterpret_cast<uint2*>(ws + kTcKr + tc_kr_off(r, lane >> 1) + (lane & 1) * 8) = kr;
+            else
+                *reinterpret_cast<uint2*>(ws + kWsKr + (r * kD + c4) * 2) = kr;
+        }
+    }
+    __syncwarp();
+
+    // ---- L = fp16(kd ki^T) masked * fp16(beta), Mqk = bf16(qd ki^T) masked: mma.sync m16n8k16
+    //      bf16 -> fp32, operand fragments fetched with conflict-free 32-bit loads ----
+    {
+        const int g = lane >> 2, t = lane & 3;
+        float l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
+        float m0[4] = {0.f, 0.f, 0.f, 0.f}, m1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < kD / 16; ++j) {
+            const int col = 16 * j + 2 * t;
+            const uint32_t b00 = *reinterpret_cast<const uint32_t*>(&sm.ki[g][col]);
+            const uint32_t b01 = *reinterpret_cast<const uint32_t*>(&sm.ki[g][col + 8]);
+            const uint32_t b10 = *reinterpret_cast<const uint32_t*>(&sm.ki[g + 8][col]);
+            const uint32_t b11 = *reinterpret_cast<const uint32_t*>(&sm.ki[g + 8][col + 8]);
+            {
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.kd[g][col]);
+                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.kd[g + 8][col]);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.kd[g][col + 8]);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.kd[g + 8][col + 8]);
+                mma_bf16_f32acc(l0, a0, a1, a2, a3, b00, b01);  // columns 0-7
+                mma_bf16_f32acc(l1, a0, a1, a2, a3, b10, b11);  // columns 8-15
+            }
+            {
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.qd[g][col]);
+                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.qd[g + 8][col]);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.qd[g][col + 8]);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.qd[g + 8][col + 8]);
+                mma_bf16_f32acc(m0, a0, a1, a2, a3, b00, b01);
+                mma_bf16_f32acc(m1, a0, a1, a2, a3, b10, b11);
+            }
+        }
+        // fragment element e of n-tile nt: row = g + 8*(e>>1), column = 8*nt + 2*t + (e&1)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                const int i = g + 8 * hr, j = 8 * nt + 2 * t;
+                const float x0 = nt ? l1[2 * hr] : l0[2 * hr], x1 = nt ? l1[2 * hr + 1] : l0[2 * hr + 1];
+                const float y0 = nt ? m1[2 * hr] : m0[2 * hr], y1 = nt ? m1[2 * hr + 1] : m0[2 * hr + 1];
+                const __half bh = __float2half_rn(sm.beta_act[i]);
+                const __half h0 = (i > j) ? __hmul(__float2half_rn(x0), bh) : __float2half_rn(0.0f);
+                const __half h1 = (i > j + 1) ? __hmul(__float2half_rn(x1), bh) : __float2half_rn(0.0f);
+                *reinterpret_cast<__half2*>(&sm.L[i][j]) = __halves2half2(h0, h1);
+                const uint32_t m = pack_bf2((i >= j) ? y0 : 0.0f, (i >= j + 1) ? y1 : 0.0f);
+                if constexpr (kTc)
+                    *reinterpret_cast<uint32_t*>(ws + kTcMqk + tc_sq_off(i, j)) = m;
+                else
+                    *reinterpret_cast<uint32_t*>(ws + kWsMqk + (i * kChunk + j) * 2) = m;
+            }
+        }
+    }
+    __syncwarp();
+    neumann_inverse_warp<kTc>(&sm.L[0][0], &sm.W[0][0], kPwLd16, ws + (kTc ? kTcInv : kWsInv), lane);
+    __syncwarp();  // the tiles may be overwritten by the next chunk
+}
+
+// Grid-stride kernel: warp w of the grid takes (chunk, head) pairs w, w + W, ... with the head index
+// fastest, so that neighbouring warps read neighbouring 256-byte rows.
+constexpr int kPwWarpsPerCta = 15;
+template <bool kTc>
+__global__ void __launch_bounds__(kPwWarpsPerCta * 32, 1) prepare_warp_kernel(const __grid_constant__ TwoPassArgs a) {
+    extern __shared__ __align__(16) uint8_t pw_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    PrepWarpSmem& sm = reinterpret_cast<PrepWarpSmem*>(pw_smem)[warp];
+    const int64_t n_units = a.total_tiles * a.H;
+    const int64_t stride = (int64_t)gridDim.x * kPwWarpsPerCta;
+    for (int64_t u = (int64_t)blockIdx.x * kPwWarpsPerCta + warp; u < n_units; u += stride) {
+        const int64_t tile = u / a.H;
+        const int h = (int)(u - tile * a.H);
+        int64_t t0;
+        int len;
+        if (!locate_tile(a, tile, &t0, &len)) continue;
+        uint8_t* ws = a.workspace + ((int64_t)h * a.total_tiles + tile) * (int64_t)(kTc ? kTcRecord : kWsRecord);
+        prepare_chunk_warp<kTc>(a, t0, len, h, ws, sm, lane);
+    }
+}
+
+template <bool kTc>
+inline int launch_prepare_warp(const TwoPassArgs& a, cudaStream_t stream) {
+    const int smem = (int)sizeof(PrepWarpSmem) * kPwWarpsPerCta;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaFuncSetAttribute(prepare_warp_kernel<kTc>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return FKDA_ERR_LAUNCH;
+    const int64_t n_units = a.total_tiles * a.H;
+    int64_t ctas = (n_units + kPwWarpsPerCta - 1) / kPwWarpsPerCta;
+    if (ctas > sms) ctas = sms;
+    if (ctas < 1) ctas = 1;
+    prepare_warp_kernel<kTc><<<(unsigned)ctas, kPwWarpsPerCta * 32, smem, stream>>>(a);
+    return FKDA_OK;
+}
+
+}  // namespace fkda

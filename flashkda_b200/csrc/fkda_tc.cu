@@ -23,7 +23,7 @@
 
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
-#include "fkda_prepare.cuh"
+#include "fkda_prepare_warp.cuh"
 #include "fkda_sm100.cuh"
 
 namespace fkda {
@@ -534,8 +534,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {
-        dim3 grid1((unsigned)a.total_tiles, (unsigned)p.H);
-        prepare_kernel<true><<<grid1, 256, 0, stream>>>(a);
+        if (launch_prepare_warp<true>(a, stream) != FKDA_OK) return FKDA_ERR_LAUNCH;
         ++launches;
     }
     if (do_rec) {

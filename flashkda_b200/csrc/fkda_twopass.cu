@@ -9,7 +9,7 @@
 // The fused tensor-core kernel is checked against it on the device.
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
-#include "fkda_prepare.cuh"
+#include "fkda_prepare_warp.cuh"
 
 namespace fkda {
 
@@ -257,8 +257,7 @@ int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launche
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {
-        dim3 grid1((unsigned)a.total_tiles, (unsigned)p.H);
-        prepare_kernel<false><<<grid1, 256, 0, stream>>>(a);
+        if (launch_prepare_warp<false>(a, stream) != FKDA_OK) return FKDA_ERR_LAUNCH;
         ++launches;
     }
     // per device and cheap, so set on every call rather than cached per process
