@@ -192,12 +192,27 @@ def run_ours(a):
         dist.init_process_group("nccl", device_id=dev)
 
     w = config(a.workload)
-    inp = make_inputs(w, device=dev, seed=rank)
+    # One long sequence (cfg5) on several GPUs: context parallel, every rank holds T / N tokens
+    # (strong scaling, one all-gather of the per-shard state maps per step).
+    cp_mode = w.name == "cfg5" and world > 1
+    if cp_mode:
+        from flashkda_b200 import cp
+        from flashkda_b200.synth import Workload
+        w_local = Workload("cfg5-shard", 1, w.T // world // 16 * 16, w.H, lower_bound=w.lower_bound,
+                           state_out=w.state_out)
+        inp = make_inputs(w_local, device=dev, seed=rank)
+    else:
+        w_local = w
+        inp = make_inputs(w, device=dev, seed=rank)
     algo = a.algo or flashkda_b200.default_algo()
-    ws_bytes = flashkda_b200.get_workspace_size(w.tokens, w.H, w.n_seqs, algo=algo)
+    ws_bytes = flashkda_b200.get_workspace_size(w_local.tokens, w.H, w_local.n_seqs, algo=algo)
     workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
 
     def step(phase_mask=0):
+        if cp_mode:
+            cp.fwd_context_parallel(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
+                                    inp["A_log"], inp["dt_bias"], inp["lower_bound"], None, inp["final_state"])
+            return
         flashkda_b200.fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
                           A_log=inp["A_log"], dt_bias=inp["dt_bias"], lower_bound=inp["lower_bound"],
                           initial_state=inp["initial_state"], final_state=inp["final_state"],
@@ -232,28 +247,31 @@ def run_ours(a):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_step = ms_total / a.steps
-    value = world * w.tokens / (ms_step * 1e-3)
+    value = world * w_local.tokens / (ms_step * 1e-3)
 
     # ---- dominant kernel alone (CUDA events on the launching stream) ----
     kernel_name = {"twopass": "fkda::recurrence_kernel"}.get(algo, "fkda::recurrence_tc_kernel")
     kernel_ms = None
     n_phase = 3
     barrier()
-    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    step(_lib.PHASE_RECURRENCE)
-    torch.cuda.synchronize(dev)
-    p0.record()
-    for _ in range(n_phase):
+    if not cp_mode:
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         step(_lib.PHASE_RECURRENCE)
-    p1.record()
-    torch.cuda.synchronize(dev)
-    kernel_ms = p0.elapsed_time(p1) / n_phase
-    step()  # leave the workspace and outputs consistent
-    torch.cuda.synchronize(dev)
+        torch.cuda.synchronize(dev)
+        p0.record()
+        for _ in range(n_phase):
+            step(_lib.PHASE_RECURRENCE)
+        p1.record()
+        torch.cuda.synchronize(dev)
+        kernel_ms = p0.elapsed_time(p1) / n_phase
+        step()  # leave the workspace and outputs consistent
+        torch.cuda.synchronize(dev)
+    else:
+        kernel_ms = ms_step  # several forward calls per step: the roofline line is then for the whole step
 
     # ---- end to end through the host-buffer API ----
     e2e = None
-    if not a.no_e2e:
+    if not a.no_e2e and not cp_mode:
         e2e = measure_e2e(a, w, inp, dev, world, algo, fwd_host)
 
     if world > 1:
@@ -268,7 +286,7 @@ def run_ours(a):
         peak_gbs, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak_gbs, peak_src = 6650.0, "fallback"
-    alg_bytes = algorithmic_bytes(w)
+    alg_bytes = algorithmic_bytes(w_local) * (world if cp_mode else 1)
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -285,10 +303,11 @@ def run_ours(a):
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": config_dict(w, algo),
-        "tflops": world * algorithmic_flops(w) / (ms_step * 1e-3) / 1e12,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if cp_mode else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": dict(config_dict(w, algo), **({"sharding": "context parallel: T/N tokens per GPU, NCCL all-gather "
+                                                 "of per-shard state maps"} if cp_mode else {})),
+        "tflops": world * algorithmic_flops(w_local) / (ms_step * 1e-3) / 1e12,
         "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                      "frac": achieved / peak_gbs, "peak_source": peak_src, "traffic": traffic,
                      "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": alg_bytes,

@@ -1,0 +1,140 @@
+"""Context parallelism for one long sequence: every rank holds a contiguous shard of the tokens.
+
+The reference has no multi-GPU path (its FLA adapter rejects context parallelism,
+fla/ops/kda/backends/flashkda.py:82-83); this module adds one on top of the forward operator.
+
+One chunk of the recurrence is affine in the state: with the state kept as S[V, K],
+``S_out = S_in @ M + N`` where the K x K transition ``M`` depends on q-independent chunk data only
+(k, g, beta) and ``N`` is linear in v.  A shard composes to one such pair, which the ordinary
+forward operator yields directly: ``N`` is the final state of the shard started from zero, ``M`` is
+the final state of the same shard run with ``v = 0`` from the identity.  So
+
+  1. rank 0 runs its shard for real (its final state is exact); ranks 1 .. G-2 compute (M_r, N_r)
+     with two forward calls on two CUDA streams (a single sequence leaves most of the GPU idle, so
+     the two calls overlap); the last rank needs no map;
+  2. one all-gather (torch.distributed: NCCL over NVLink on GPUs, gloo in CPU tests) of the fp32
+     pairs, 2 * H * 128 * 128 * 4 bytes per rank;
+  3. every rank folds its predecessors in order, ``S <- S @ M_j + N_j`` (fp32), to get its true
+     initial state, then runs the ordinary forward on its shard; the last rank's final state is the
+     sequence's final state.
+
+Shard boundaries must be multiples of 16 tokens (every shard but the last), so that the chunk grid
+of the sharded run equals that of the one-shot run.  The maps carry the bf16 roundings of the
+kernel, so the result matches a single-GPU run to the parity tolerances (out max-abs 2e-2, state
+RMSE-ratio 1e-2), not bit for bit.
+"""
+from typing import Callable, List, Optional, Tuple
+
+import torch
+
+D = 128
+
+
+def shard_maps(fwd_fn: Callable, q, k, v, g, beta, scale, A_log, dt_bias, lower_bound, need_transition=True,
+               streams=None) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """(M, N) of one shard, both fp32 ``[1, H, 128, 128]``: ``S_out = S_in @ M + N`` (S as [V, K])."""
+    H = q.shape[2]
+    dev = q.device
+    N = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
+    M = None
+    scratch = torch.empty_like(v)
+    if need_transition:
+        M = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
+        eye = torch.eye(D, dtype=torch.float32, device=dev).expand(1, H, D, D).contiguous()
+        zero_v = torch.zeros_like(v)
+        scratch2 = torch.empty_like(v)
+    if streams is not None and need_transition:
+        cur = torch.cuda.current_stream(dev)
+        s0, s1 = streams
+        s0.wait_stream(cur)
+        s1.wait_stream(cur)
+        with torch.cuda.stream(s0):
+            fwd_fn(q, k, v, g, beta, scale, scratch, A_log, dt_bias, lower_bound, None, N, None)
+        with torch.cuda.stream(s1):
+            fwd_fn(q, k, zero_v, g, beta, scale, scratch2, A_log, dt_bias, lower_bound, eye, M, None)
+        cur.wait_stream(s0)
+        cur.wait_stream(s1)
+        for t in (scratch, scratch2, zero_v, eye):
+            t.record_stream(s0)
+            t.record_stream(s1)
+    else:
+        fwd_fn(q, k, v, g, beta, scale, scratch, A_log, dt_bias, lower_bound, None, N, None)
+        if need_transition:
+            fwd_fn(q, k, zero_v, g, beta, scale, scratch2, A_log, dt_bias, lower_bound, eye, M, None)
+    return M, N
+
+
+def fold_initial_state(first_end_state: torch.Tensor, maps: List[Tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
+    """State entering the shard that follows rank 0 and the shards of ``maps`` (in order)."""
+    S = first_end_state.to(torch.float32)
+    for M, N in maps:
+        S = torch.matmul(S, M) + N
+    return S
+
+
+def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None,
+                         final_state=None, group=None, fwd_fn: Callable = None):
+    """Forward over one sequence sharded across the ranks of ``group`` (contiguous shards in rank
+    order, B = 1, every shard but the last a multiple of 16 tokens).  ``initial_state`` is used by
+    rank 0; ``final_state`` (optional, any rank) receives the state after the last token.
+    Writes this rank's ``out`` in place."""
+    import torch.distributed as dist
+    if fwd_fn is None:
+        from . import fwd as fwd_fn
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    assert q.shape[0] == 1, "context parallelism shards ONE sequence (B must be 1)"
+    if rank < world - 1:
+        assert q.shape[1] % 16 == 0, "every shard but the last must hold a multiple of 16 tokens"
+    H, dev = q.shape[2], q.device
+    payload = torch.zeros(2, 1, H, D, D, dtype=torch.float32, device=dev)
+    if world == 1:
+        fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, final_state, None)
+        return
+    if rank == 0:
+        end = payload[1]
+        fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, end, None)
+    elif rank < world - 1:
+        streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev)) if dev.type == "cuda" else None
+        M, N = shard_maps(fwd_fn, q, k, v, g, beta, scale, A_log, dt_bias, lower_bound, True, streams)
+        payload[0].copy_(M)
+        payload[1].copy_(N)
+    gathered = [torch.empty_like(payload) for _ in range(world)]
+    dist.all_gather(gathered, payload, group=group)
+    last_state = None
+    if rank > 0:
+        S_in = fold_initial_state(gathered[0][1], [(gathered[j][0], gathered[j][1]) for j in range(1, rank)])
+        if rank == world - 1:
+            last_state = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
+        fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, S_in.contiguous(), last_state, None)
+    if final_state is not None:
+        buf = last_state if rank == world - 1 else torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
+        dist.broadcast(buf, src=dist.get_global_rank(group, world - 1) if group is not None else world - 1, group=group)
+        final_state.copy_(buf.to(final_state.dtype))
+
+
+def fwd_sharded_emulated(n_shards: int, q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound,
+                         initial_state=None, final_state=None, fwd_fn: Callable = None):
+    """The same algorithm with all shards in one process (no process group): used to check the
+    numerics of the map-and-fold scheme on a single device."""
+    if fwd_fn is None:
+        from . import fwd as fwd_fn
+    T = q.shape[1]
+    per = (T // n_shards) // 16 * 16
+    bounds = [i * per for i in range(n_shards)] + [T]
+    sl = lambda x, i: x[:, bounds[i]:bounds[i + 1]].contiguous()
+    H, dev = q.shape[2], q.device
+    outs = [torch.empty_like(sl(v, i)) for i in range(n_shards)]
+    end0 = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
+    fwd_fn(sl(q, 0), sl(k, 0), sl(v, 0), sl(g, 0), sl(beta, 0), scale, outs[0], A_log, dt_bias, lower_bound,
+           initial_state, end0, None)
+    maps = [shard_maps(fwd_fn, sl(q, i), sl(k, i), sl(v, i), sl(g, i), sl(beta, i), scale, A_log, dt_bias,
+                       lower_bound) for i in range(1, n_shards - 1)]
+    last = end0
+    for i in range(1, n_shards):
+        S_in = fold_initial_state(end0, maps[:i - 1]).contiguous()
+        last = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
+        fwd_fn(sl(q, i), sl(k, i), sl(v, i), sl(g, i), sl(beta, i), scale, outs[i], A_log, dt_bias, lower_bound,
+               S_in, last, None)
+    out.copy_(torch.cat(outs, dim=1))
+    if final_state is not None:
+        final_state.copy_(last.to(final_state.dtype))

@@ -1,0 +1,111 @@
+"""Context parallelism (one long sequence sharded over ranks): host logic on CPU with gloo process
+groups (world sizes 2 and 3, the CPU oracle standing in for the device operator), and the numerics of
+the map-and-fold scheme on one GPU with all shards in one process."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from flashkda_b200 import cp
+from flashkda_b200.synth import Workload, make_inputs, to_device
+from kda_testlib import run_oracle
+
+
+def _weak_decay_inputs(T, H, seed):
+    """Weak gates (A_log = log 0.05, lower_bound -0.02) so that the transition M of a shard is far from
+    zero and the fold really matters; strong default gates would hide a wrong M."""
+    w = Workload("cp", 1, T, H, lower_bound=-0.02, state_in="fp32", state_out="fp32")
+    inp = make_inputs(w, seed=seed)
+    inp["A_log"] = torch.full_like(inp["A_log"], -3.0)
+    return inp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _cp_worker(rank, world, port, T, H, seed, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(2)
+    inp = _weak_decay_inputs(T, H, seed)
+    per = (T // world) // 16 * 16
+    lo, hi = rank * per, (T if rank == world - 1 else (rank + 1) * per)
+    sh = {key: inp[key][:, lo:hi].contiguous() for key in ("q", "k", "v", "g", "beta")}
+    out = torch.zeros_like(sh["v"])
+    hT = torch.zeros_like(inp["final_state"])
+    cp.fwd_context_parallel(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], inp["scale"], out, inp["A_log"],
+                            inp["dt_bias"], inp["lower_bound"], initial_state=inp["initial_state"], final_state=hT,
+                            fwd_fn=oracle.fwd)
+    ret[rank] = (lo, hi, out, hT)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_context_parallel_gloo(world):
+    T, H, seed = 400, 2, 31
+    inp = _weak_decay_inputs(T, H, seed)
+    ref_out, ref_hT = run_oracle(inp)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_cp_worker, args=(world, _free_port(), T, H, seed, ret), nprocs=world, join=True)
+    out = torch.zeros_like(ref_out)
+    for r in range(world):
+        lo, hi, o, hT = ret[r]
+        out[:, lo:hi] = o
+        assert oracle.err_ratio(ref_hT, hT) <= 1e-2, f"rank {r} final_state"
+    assert oracle.max_abs(ref_out, out) <= 2e-2
+    assert oracle.err_ratio(ref_out, out) <= 1e-2
+    # rank 0's shard is computed exactly as in the one-shot run
+    lo, hi, o, _ = ret[0]
+    assert torch.equal(o, ref_out[:, lo:hi])
+
+
+def test_fold_is_needed_with_weak_decay():
+    """Sanity of the test itself: dropping the transition M changes the result visibly."""
+    inp = _weak_decay_inputs(256, 1, 5)
+    half = {key: inp[key][:, 128:].contiguous() for key in ("q", "k", "v", "g", "beta")}
+    M, N = cp.shard_maps(oracle.fwd, half["q"], half["k"], half["v"], half["g"], half["beta"], inp["scale"],
+                         inp["A_log"], inp["dt_bias"], inp["lower_bound"])
+    assert M.abs().max() > 0.05
+    S = torch.randn(1, 1, 128, 128) * 0.05
+    assert oracle.err_ratio(cp.fold_initial_state(S, [(M, N)]), N) > 1e-2
+
+
+def test_emulated_shards_match_one_shot_cpu():
+    inp = _weak_decay_inputs(512, 2, 9)
+    ref_out, ref_hT = run_oracle(inp)
+    out = torch.zeros_like(ref_out)
+    hT = torch.zeros_like(ref_hT)
+    cp.fwd_sharded_emulated(4, inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], out, inp["A_log"],
+                            inp["dt_bias"], inp["lower_bound"], inp["initial_state"], hT, fwd_fn=oracle.fwd)
+    assert oracle.err_ratio(ref_out, out) <= 1e-2
+    assert oracle.err_ratio(ref_hT, hT) <= 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shards", [2, 4, 8])
+def test_emulated_shards_match_one_shot_gpu(shards):
+    import flashkda_b200
+    inp = to_device(_weak_decay_inputs(4096, 4, 17), "cuda")
+    one_out, one_hT = torch.zeros_like(inp["out"]), torch.zeros_like(inp["final_state"])
+    flashkda_b200.fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], one_out, inp["A_log"],
+                      inp["dt_bias"], inp["lower_bound"], inp["initial_state"], one_hT)
+    out, hT = torch.zeros_like(one_out), torch.zeros_like(one_hT)
+    cp.fwd_sharded_emulated(shards, inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], out,
+                            inp["A_log"], inp["dt_bias"], inp["lower_bound"], inp["initial_state"], hT)
+    torch.cuda.synchronize()
+    print(f"shards {shards}: out ratio {oracle.err_ratio(one_out, out):.3e} state ratio {oracle.err_ratio(one_hT, hT):.3e}")
+    assert oracle.max_abs(one_out, out) <= 2e-2
+    assert oracle.err_ratio(one_out, out) <= 1e-2
+    assert oracle.err_ratio(one_hT, hT) <= 1e-2
