@@ -249,25 +249,32 @@ def run_ours(a):
     ms_step = ms_total / a.steps
     value = world * w_local.tokens / (ms_step * 1e-3)
 
-    # ---- dominant kernel alone (CUDA events on the launching stream) ----
-    kernel_name = {"twopass": "fkda::recurrence_kernel"}.get(algo, "fkda::recurrence_tc_kernel")
-    kernel_ms = None
+    # ---- each kernel of the forward alone (CUDA events on the launching stream); the slower one is
+    #      the dominant kernel the roofline line describes ----
+    names = {"twopass": ("fkda::prepare_warp_kernel", "fkda::recurrence_kernel")}.get(
+        algo, ("fkda::prepare_warp_kernel", "fkda::recurrence_tc_kernel"))
+    kernel_times = {}
     n_phase = 3
     barrier()
     if not cp_mode:
-        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        step(_lib.PHASE_RECURRENCE)
-        torch.cuda.synchronize(dev)
-        p0.record()
-        for _ in range(n_phase):
-            step(_lib.PHASE_RECURRENCE)
-        p1.record()
-        torch.cuda.synchronize(dev)
-        kernel_ms = p0.elapsed_time(p1) / n_phase
+        step()
+        for name, mask in zip(names, (_lib.PHASE_PREPARE, _lib.PHASE_RECURRENCE)):
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            step(mask)
+            torch.cuda.synchronize(dev)
+            p0.record()
+            for _ in range(n_phase):
+                step(mask)
+            p1.record()
+            torch.cuda.synchronize(dev)
+            kernel_times[name] = p0.elapsed_time(p1) / n_phase
         step()  # leave the workspace and outputs consistent
         torch.cuda.synchronize(dev)
+        kernel_name = max(kernel_times, key=kernel_times.get)
+        kernel_ms = kernel_times[kernel_name]
     else:
-        kernel_ms = ms_step  # several forward calls per step: the roofline line is then for the whole step
+        kernel_name = "whole context-parallel step (several forward calls)"
+        kernel_ms = ms_step
 
     # ---- end to end through the host-buffer API ----
     e2e = None
@@ -291,7 +298,9 @@ def run_ours(a):
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
-        traffic = json.load(open(tpath)).get(f"{algo}:{w.name}")
+        per_unit = json.load(open(tpath)).get(kernel_name, {}).get("bytes_per_unit")
+        if per_unit is not None:  # scaled from the small ncu capture by the (chunk, head) units of this launch
+            traffic = per_unit * ((w_local.tokens + 15) // 16) * w.H
 
     cpu = None
     if not a.no_cpu and world == 1:
@@ -310,7 +319,7 @@ def run_ours(a):
         "tflops": world * algorithmic_flops(w_local) / (ms_step * 1e-3) / 1e12,
         "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
                      "frac": achieved / peak_gbs, "peak_source": peak_src, "traffic": traffic,
-                     "kernel_ms": kernel_ms, "algorithmic_bytes_per_launch": alg_bytes,
+                     "kernel_ms": kernel_ms, "kernels_ms": kernel_times, "algorithmic_bytes_per_launch": alg_bytes,
                      "whole_forward_frac": alg_bytes / (ms_step * 1e-3) / 1e9 / peak_gbs},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * a.steps, "clocks": clocks,
     }
