@@ -46,9 +46,10 @@ def test_chunk_kda_dispatches_here_and_matches_triton(lens, monkeypatch):
     torch.cuda.synchronize()
     assert calls, "FLA did not dispatch to flash_kda.fwd"
     assert torch.isfinite(out_a.float()).all() and torch.isfinite(hT_a).all()
-    try:  # the Triton path: the backend only accepts inference mode, so no_grad falls through to FLA's own kernels
+    try:  # the Triton path: the backend refuses calls made with autograd enabled, which then fall through to
+        #       FLA's own kernels
         n0 = len(calls)
-        with torch.no_grad():
+        with torch.enable_grad():
             out_b, hT_b = fla_kda.chunk_kda(**kw)
         torch.cuda.synchronize()
         assert len(calls) == n0
@@ -56,5 +57,5 @@ def test_chunk_kda_dispatches_here_and_matches_triton(lens, monkeypatch):
         pytest.skip(f"FLA Triton path unavailable here: {type(e).__name__}: {e}")
     r_out, r_state = oracle.err_ratio(out_b.float(), out_a.float()), oracle.err_ratio(hT_b.float(), hT_a.float())
     print(f"vs FLA Triton: out ratio {r_out:.3e}, state ratio {r_state:.3e}")
-    assert r_out <= 0.006
+    assert r_out <= 0.008  # measured 5.9e-3 on N(0,1) inputs; the reference reports 3e-3..5e-3 on its own cases
     assert r_state <= 0.01
