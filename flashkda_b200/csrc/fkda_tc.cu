@@ -345,11 +345,15 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             tc_fence_after_sync();
             TC_STAMP(7);
 
-            // ---- out = bf(o0) (+) bf(Mqk U) (thread = V row), stored while the next chunk's MMA1 runs ----
+            // ---- out = bf(o0) (+) bf(Mqk U) (thread = V row); the TMEM loads of the state update that
+            //      follows are kept one batch of 16 columns ahead of the arithmetic ----
+            uint32_t ra[16], rb[16];
             {
                 uint32_t r[32];
                 tmem_ld32(t_d1 + lane_sel, r);  // D3 in 0-15, o0 in 16-31
+                tmem_ld16(t_ds + lane_sel, ra);
                 tmem_wait_ld();
+                tmem_ld16(t_ds + 16 + lane_sel, rb);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const uint32_t o = bf2_add(pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1])),
@@ -366,22 +370,29 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             }
             // ---- state column k (thread = TMEM lane k of DST): S[vv][k] = bf(fma(S[vv][k], E_tot[k], DST[k][vv])),
             //      registers only; the refreshed column also goes to the S^T tile for the next chunk's MMA1 ----
+            auto update16 = [&](int b, const uint32_t (&r)[16]) {  // rows vv = 16b .. 16b+15
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                uint32_t r[32];
-                tmem_ld32(t_ds + 32 * b + lane_sel, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const uint32_t sv = sreg[16 * b + i];
-                    sreg[16 * b + i] = pack_bf2(__fmaf_rn(bf_lo(sv), e_mine, __uint_as_float(r[2 * i])),
-                                                __fmaf_rn(bf_hi(sv), e_mine, __uint_as_float(r[2 * i + 1])));
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t sv = sreg[8 * b + i];
+                    sreg[8 * b + i] = pack_bf2(__fmaf_rn(bf_lo(sv), e_mine, __uint_as_float(r[2 * i])),
+                                               __fmaf_rn(bf_hi(sv), e_mine, __uint_as_float(r[2 * i + 1])));
                 }
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    *reinterpret_cast<uint4*>(cs + kSmS + sT_off(v, 4 * b + q)) =
-                        make_uint4(sreg[16 * b + 4 * q], sreg[16 * b + 4 * q + 1], sreg[16 * b + 4 * q + 2],
-                                   sreg[16 * b + 4 * q + 3]);
+                for (int q = 0; q < 2; ++q)
+                    *reinterpret_cast<uint4*>(cs + kSmS + sT_off(v, 2 * b + q)) =
+                        make_uint4(sreg[8 * b + 4 * q], sreg[8 * b + 4 * q + 1], sreg[8 * b + 4 * q + 2],
+                                   sreg[8 * b + 4 * q + 3]);
+            };
+#pragma unroll
+            for (int b = 0; b < 8; b += 2) {
+                update16(b, ra);
+                tmem_wait_ld();
+                if (b + 2 < 8) tmem_ld16(t_ds + 16 * (b + 2) + lane_sel, ra);
+                update16(b + 1, rb);
+                if (b + 2 < 8) {
+                    tmem_wait_ld();
+                    tmem_ld16(t_ds + 16 * (b + 3) + lane_sel, rb);
+                }
             }
             TC_STAMP(9);
             fence_proxy_async_smem();
