@@ -28,21 +28,28 @@ constexpr int kWsRecord = kWsMqk + kChunk * kChunk * 2;  // 13824
 static_assert(kWsRecord == 13824, "workspace record size");
 
 // Record of the tensor-core two-pass workspace: operand tiles in the no-swizzle UMMA canonical
-// layouts (8 x 16-byte "core matrices" of 128 contiguous bytes):
-//   B1  [kd; qd] as the K-major B operand [32 rows, K=128]: byte = (k/8)*512 + (r/8)*128 + (r%8)*16 + (k%8)*2
-//   KR  kr as the MN-major B operand [N=128, K=16 tokens]:  byte = (i/8)*2048 + (n/8)*128 + (i%8)*16 + (n%8)*2
+// layouts (8 x 16-byte "core matrices" of 128 contiguous bytes).  The strides between core matrices are
+// padded by 16 bytes so that the prepare stage, whose lanes own columns, fills the same tiles in shared
+// memory without bank conflicts and ships them with bulk copies:
+//   B1  [kd; qd] as the K-major B operand [32 rows, K=128]: byte = (k/8)*528 + (r/8)*128 + (r%8)*16 + (k%8)*2
+//   KR  kr as the MN-major operand [128 k, 16 tokens]:      byte = (i/8)*2304 + (n/8)*144 + (i%8)*16 + (n%8)*2
 //   INV, MQK as K-major B operands [16, 16]:                byte = (j/8)*256 + (i/8)*128 + (i%8)*16 + (j%8)*2
 //   ET  E_tot [128] f32;  BETA bf16-rounded sigmoid(beta) [16] widened to f32
+constexpr int kTcB1Lbo = 528;                   // between the 16-byte K chunks of B1
+constexpr int kTcB1Bytes = 16 * kTcB1Lbo;       // 8448
+constexpr int kTcKrSbo = 144;                   // between 8-column groups of KR
+constexpr int kTcKrLbo = 16 * kTcKrSbo;         // 2304, between the two 8-token groups
+constexpr int kTcKrBytes = 2 * kTcKrLbo;        // 4608
 constexpr int kTcB1 = 0;
-constexpr int kTcKr = 8192;
-constexpr int kTcInv = 12288;
-constexpr int kTcMqk = 12800;
-constexpr int kTcEt = 13312;
-constexpr int kTcBeta = 13824;
-constexpr int kTcRecord = 13888;
+constexpr int kTcKr = kTcB1 + kTcB1Bytes;       // 8448
+constexpr int kTcInv = kTcKr + kTcKrBytes;      // 13056
+constexpr int kTcMqk = kTcInv + 512;            // 13568
+constexpr int kTcEt = kTcMqk + 512;             // 14080
+constexpr int kTcBeta = kTcEt + 512;            // 14592
+constexpr int kTcRecord = kTcBeta + 64;         // 14656
 static_assert(kTcRecord % 16 == 0, "bulk copies move multiples of 16 bytes");
-__host__ __device__ constexpr int tc_b1_off(int r, int kc) { return kc * 512 + (r >> 3) * 128 + (r & 7) * 16; }
-__host__ __device__ constexpr int tc_kr_off(int i, int nc) { return (i >> 3) * 2048 + nc * 128 + (i & 7) * 16; }
+__host__ __device__ constexpr int tc_b1_off(int r, int kc) { return kc * kTcB1Lbo + (r >> 3) * 128 + (r & 7) * 16; }
+__host__ __device__ constexpr int tc_kr_off(int i, int nc) { return (i >> 3) * kTcKrLbo + nc * kTcKrSbo + (i & 7) * 16; }
 __host__ __device__ constexpr int tc_sq_off(int i, int j) {
     return (j >> 3) * 256 + (i >> 3) * 128 + (i & 7) * 16 + (j & 7) * 2;
 }

@@ -10,20 +10,25 @@
 
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
+#include "fkda_sm100.cuh"
 
 namespace fkda {
 
-constexpr int kPwPitch = kD + 8;  // bf16 row pitch (272 B): conflict-free fragment loads
-constexpr int kPwLd16 = 24;       // fp16 row pitch of the 16x16 matrices
+constexpr int kPwLd16 = 24;   // fp16 row pitch of the 16x16 matrices
+constexpr int kPwKiLbo = 272;  // ki tile: K-major core matrices, 16-byte K chunks 272 bytes apart (256 + 16 padding)
 
-struct PrepWarpSmem {
-    __nv_bfloat16 kd[kChunk][kPwPitch];  // k * 2^G
-    __nv_bfloat16 qd[kChunk][kPwPitch];  // q * 2^G * scale
-    __nv_bfloat16 ki[kChunk][kPwPitch];  // k * 2^-G
+// Per-warp shared memory.  b1 is the B1 part of the record ([kd; qd] in its final UMMA layout, see
+// fkda_common.cuh); kikr first holds ki (K-major core matrices: byte = (k/8)*272 + (r/8)*128 + (r%8)*16 +
+// (k%8)*2) for the in-chunk products and then kr in the record's KR layout.  Both are shipped to the
+// workspace with bulk copies; the padded strides keep the column-owning lanes free of bank conflicts.
+struct alignas(16) PrepWarpSmem {
+    uint8_t b1[kTcB1Bytes];
+    uint8_t kikr[kTcKrBytes];
     __half L[kChunk][kPwLd16];
     __half W[kChunk][kPwLd16];
     float beta_act[kChunk];
 };
+static_assert(16 * kPwKiLbo <= kTcKrBytes, "the ki tile fits the KR buffer");
 
 // Where chunk `tile` of the (possibly ragged) batch lives: first token and number of valid rows.
 // Returns false for a tile index past the last chunk (ragged upper bound).
@@ -137,36 +142,24 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         const uint32_t em1 = pack_bf2(ex2_approx(-csum[2]), ex2_approx(-csum[3]));
         const uint2 kd = make_uint2(bf2_mul(kn0, ep0), bf2_mul(kn1, ep1));
         const uint2 qd = make_uint2(bf2_mul(bf2_mul(qn0, ep0), sc2), bf2_mul(bf2_mul(qn1, ep1), sc2));
-        *reinterpret_cast<uint2*>(&sm.kd[r][c4]) = kd;
-        *reinterpret_cast<uint2*>(&sm.qd[r][c4]) = qd;
-        *reinterpret_cast<uint2*>(&sm.ki[r][c4]) = make_uint2(bf2_mul(kn0, em0), bf2_mul(kn1, em1));
-        if constexpr (kTc) {
+        {
             const int off = tc_b1_off(r, lane >> 1) + (lane & 1) * 8;
-            *reinterpret_cast<uint2*>(ws + kTcB1 + off) = kd;
-            *reinterpret_cast<uint2*>(ws + kTcB1 + off + 2 * 128) = qd;  // rows 16..31 = two row groups further
-        } else {
+            *reinterpret_cast<uint2*>(sm.b1 + off) = kd;
+            *reinterpret_cast<uint2*>(sm.b1 + off + 2 * 128) = qd;  // rows 16..31 = two row groups further
+            *reinterpret_cast<uint2*>(sm.kikr + (lane >> 1) * kPwKiLbo + (r >> 3) * 128 + (r & 7) * 16 + (lane & 1) * 8) =
+                make_uint2(bf2_mul(kn0, em0), bf2_mul(kn1, em1));
+        }
+        if constexpr (!kTc) {
             *reinterpret_cast<uint2*>(ws + kWsKd + (r * kD + c4) * 2) = kd;
             *reinterpret_cast<uint2*>(ws + kWsQd + (r * kD + c4) * 2) = qd;
         }
     }
     }
-    // E_tot and kr (ki read back from my own columns of the tile)
-    {
-        float et[4];
+    // E_tot now; kr = ki (*) bf(E_tot) is formed after the products have consumed the ki tile
+    float et[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) et[i] = ex2_approx(csum[i]);
-        *reinterpret_cast<float4*>(ws + (kTc ? kTcEt : kWsEt) + c4 * 4) = make_float4(et[0], et[1], et[2], et[3]);
-        const uint32_t et0 = pack_bf2(et[0], et[1]), et1 = pack_bf2(et[2], et[3]);
-#pragma unroll
-        for (int r = 0; r < kChunk; ++r) {
-            const uint2 ki = *reinterpret_cast<const uint2*>(&sm.ki[r][c4]);
-            const uint2 kr = make_uint2(bf2_mul(ki.x, et0), bf2_mul(ki.y, et1));
-            if constexpr (kTc)
-                *reinterpret_cast<uint2*>(ws + kTcKr + tc_kr_off(r, lane >> 1) + (lane & 1) * 8) = kr;
-            else
-                *reinterpret_cast<uint2*>(ws + kWsKr + (r * kD + c4) * 2) = kr;
-        }
-    }
+    for (int i = 0; i < 4; ++i) et[i] = ex2_approx(csum[i]);
+    *reinterpret_cast<float4*>(ws + (kTc ? kTcEt : kWsEt) + c4 * 4) = make_float4(et[0], et[1], et[2], et[3]);
     __syncwarp();
 
     // ---- L = fp16(kd ki^T) masked * fp16(beta), Mqk = bf16(qd ki^T) masked: mma.sync m16n8k16
@@ -177,24 +170,26 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         float m0[4] = {0.f, 0.f, 0.f, 0.f}, m1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < kD / 16; ++j) {
-            const int col = 16 * j + 2 * t;
-            const uint32_t b00 = *reinterpret_cast<const uint32_t*>(&sm.ki[g][col]);
-            const uint32_t b01 = *reinterpret_cast<const uint32_t*>(&sm.ki[g][col + 8]);
-            const uint32_t b10 = *reinterpret_cast<const uint32_t*>(&sm.ki[g + 8][col]);
-            const uint32_t b11 = *reinterpret_cast<const uint32_t*>(&sm.ki[g + 8][col + 8]);
+            // element (row, 16j + 2t [+8]) of a K-major core-matrix tile: chunk 2j [+1], row group, row, 4t bytes
+            const uint8_t* kib = sm.kikr + 2 * j * kPwKiLbo + g * 16 + 4 * t;
+            const uint32_t b00 = *reinterpret_cast<const uint32_t*>(kib);
+            const uint32_t b01 = *reinterpret_cast<const uint32_t*>(kib + kPwKiLbo);
+            const uint32_t b10 = *reinterpret_cast<const uint32_t*>(kib + 128);
+            const uint32_t b11 = *reinterpret_cast<const uint32_t*>(kib + kPwKiLbo + 128);
+            const uint8_t* ab = sm.b1 + 2 * j * kTcB1Lbo + g * 16 + 4 * t;
             {
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.kd[g][col]);
-                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.kd[g + 8][col]);
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.kd[g][col + 8]);
-                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.kd[g + 8][col + 8]);
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(ab);
+                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(ab + 128);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(ab + kTcB1Lbo);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(ab + kTcB1Lbo + 128);
                 mma_bf16_f32acc(l0, a0, a1, a2, a3, b00, b01);  // columns 0-7
                 mma_bf16_f32acc(l1, a0, a1, a2, a3, b10, b11);  // columns 8-15
             }
             {
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.qd[g][col]);
-                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.qd[g + 8][col]);
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.qd[g][col + 8]);
-                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.qd[g + 8][col + 8]);
+                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(ab + 256);  // qd = rows 16..31
+                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(ab + 256 + 128);
+                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(ab + 256 + kTcB1Lbo);
+                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(ab + 256 + kTcB1Lbo + 128);
                 mma_bf16_f32acc(m0, a0, a1, a2, a3, b00, b01);
                 mma_bf16_f32acc(m1, a0, a1, a2, a3, b10, b11);
             }
@@ -220,8 +215,39 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         }
     }
     __syncwarp();
+    // ---- kr = ki (*) bf(E_tot): read my ki columns back, then overwrite the buffer in the KR layout ----
+    {
+        const uint32_t et0 = pack_bf2(et[0], et[1]), et1 = pack_bf2(et[2], et[3]);
+        uint2 kr[kChunk];
+#pragma unroll
+        for (int r = 0; r < kChunk; ++r) {
+            const uint2 ki = *reinterpret_cast<const uint2*>(sm.kikr + (lane >> 1) * kPwKiLbo + (r >> 3) * 128 +
+                                                             (r & 7) * 16 + (lane & 1) * 8);
+            kr[r] = make_uint2(bf2_mul(ki.x, et0), bf2_mul(ki.y, et1));
+        }
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < kChunk; ++r) {
+            if constexpr (kTc)
+                *reinterpret_cast<uint2*>(sm.kikr + tc_kr_off(r, lane >> 1) + (lane & 1) * 8) = kr[r];
+            else
+                *reinterpret_cast<uint2*>(ws + kWsKr + (r * kD + c4) * 2) = kr[r];
+        }
+    }
+    if constexpr (kTc) {  // ship [kd; qd] and kr: two bulk copies shared memory -> workspace record
+        sm100::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            sm100::bulk_s2g(ws + kTcB1, sm.b1, kTcB1Bytes);
+            sm100::bulk_s2g(ws + kTcKr, sm.kikr, kTcKrBytes);
+            sm100::bulk_commit_group();
+        }
+    }
     neumann_inverse_warp<kTc>(&sm.L[0][0], &sm.W[0][0], kPwLd16, ws + (kTc ? kTcInv : kWsInv), lane);
-    __syncwarp();  // the tiles may be overwritten by the next chunk
+    if constexpr (kTc) {  // the tiles are rewritten by the next chunk: the copies must have read them
+        if (lane == 0) sm100::bulk_wait_group_read<0>();
+    }
+    __syncwarp();
 }
 
 // Grid-stride kernel: warp w of the grid takes (chunk, head) pairs w, w + W, ... with the head index
@@ -243,6 +269,7 @@ __global__ void __launch_bounds__(kPwWarpsPerCta * 32, 1) prepare_warp_kernel(co
         uint8_t* ws = a.workspace + ((int64_t)h * a.total_tiles + tile) * (int64_t)(kTc ? kTcRecord : kWsRecord);
         prepare_chunk_warp<kTc>(a, t0, len, h, ws, sm, lane);
     }
+    sm100::bulk_wait_group<0>();  // (lane 0) the last records have landed
 }
 
 template <bool kTc>

@@ -49,8 +49,9 @@ constexpr int kSmStage = 32768;                            // kTcStages chunk re
 constexpr int kSmStageBytes = kTcRecord;                   // 13888
 constexpr int kSmV = kSmStage + kTcStages * kSmStageBytes;    // kTcStages value tiles [16][128] bf16 (60544)
 constexpr int kSmA23 = kSmV + kTcStages * 4096;               // A operand of the 16-deep products [128, 16]
-constexpr int kSmOut = kSmA23 + 4096;                         // out tile [16][128] bf16
-constexpr int kSmChainBytes = kSmOut + 4096;                  // 76928
+constexpr int kSmOut = kSmA23;                                // out tile [16][128] bf16: reuses the A23 tile, which
+                                                              // is dead between the chunk's last MMA and the next E1
+constexpr int kSmChainBytes = kSmA23 + 4096;
 static_assert(kSmV % 128 == 0 && kSmOut % 128 == 0, "TMA tiles are 128-byte aligned");
 static_assert(kSmChainBytes % 128 == 0, "chain blocks stay 128-byte aligned");
 
@@ -244,11 +245,14 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
             if (wiw == 0) {
                 if (elect_one()) {
+                    // the previous out tile shares the A23 tile: its TMA store must have read it before anybody
+                    // (released by this MMA's completion) writes u' there
+                    bulk_wait_group_read<0>();
                     tc_fence_after_sync();
-                    const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, 512, 128);
+                    const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, kTcB1Lbo, 128);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        umma_ss(t_d1, s_desc0 + (uint64_t)(j * 256), bd0 + (uint64_t)(j * 64), idesc_n32, j > 0 ? 1u : 0u);
+                        umma_ss(t_d1, s_desc0 + (uint64_t)(j * 256), bd0 + (uint64_t)(j * (2 * kTcB1Lbo / 16)), idesc_n32, j > 0 ? 1u : 0u);
                     umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();
@@ -332,10 +336,9 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             // ---- MMA3: D3[V,16] = U^T . Mqk^T (over the dead u0 columns);  DST[K,V] = kr^T . U ----
             if (wiw == 0) {
                 if (elect_one()) {
-                    bulk_wait_group_read<0>();  // the previous out tile has been read by its TMA store
                     tc_fence_after_sync();
                     umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
-                    umma_ss(t_ds, make_smem_desc(st_addr + kTcKr, 2048, 128), a23_desc, idesc_dst, 0u);
+                    umma_ss(t_ds, make_smem_desc(st_addr + kTcKr, kTcKrLbo, kTcKrSbo), a23_desc, idesc_dst, 0u);
                     umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();
