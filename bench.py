@@ -53,6 +53,9 @@ def parse():
     ap.add_argument("--algo", default=None)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--seq-parts", type=int, default=1,
+                    help="single GPU, B=1: split the sequence into this many pieces that run side by side "
+                         "(flashkda_b200.cp.fwd_sequence_parallel; approximate at piece boundaries)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target duration of the CPU baseline sample")
     return ap.parse_args()
 
@@ -209,9 +212,16 @@ def run_ours(a):
     workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
 
     def step(phase_mask=0):
+        if a.seq_parts > 1 and not cp_mode:
+            from flashkda_b200 import cp as _cp
+            _cp.fwd_sequence_parallel(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
+                                      inp["A_log"], inp["dt_bias"], inp["lower_bound"], inp["initial_state"],
+                                      inp["final_state"], parts=a.seq_parts)
+            return
         if cp_mode:
             cp.fwd_context_parallel(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
-                                    inp["A_log"], inp["dt_bias"], inp["lower_bound"], None, inp["final_state"])
+                                    inp["A_log"], inp["dt_bias"], inp["lower_bound"], None, inp["final_state"],
+                                    parts=max(1, a.seq_parts))
             return
         flashkda_b200.fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
                           A_log=inp["A_log"], dt_bias=inp["dt_bias"], lower_bound=inp["lower_bound"],
@@ -256,7 +266,7 @@ def run_ours(a):
     kernel_times = {}
     n_phase = 3
     barrier()
-    if not cp_mode:
+    if not cp_mode and a.seq_parts == 1:
         step()
         for name, mask in zip(names, (_lib.PHASE_PREPARE, _lib.PHASE_RECURRENCE)):
             p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -273,7 +283,7 @@ def run_ours(a):
         kernel_name = max(kernel_times, key=kernel_times.get)
         kernel_ms = kernel_times[kernel_name]
     else:
-        kernel_name = "whole context-parallel step (several forward calls)"
+        kernel_name = "whole step (several forward calls: sequence split / context parallel)"
         kernel_ms = ms_step
 
     # ---- end to end through the host-buffer API ----

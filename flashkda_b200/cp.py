@@ -73,7 +73,7 @@ def fold_initial_state(first_end_state: torch.Tensor, maps: List[Tuple[torch.Ten
 
 
 def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None,
-                         final_state=None, group=None, fwd_fn: Callable = None):
+                         final_state=None, group=None, fwd_fn: Callable = None, parts: int = 1):
     """Forward over one sequence sharded across the ranks of ``group`` (contiguous shards in rank
     order, B = 1, every shard but the last a multiple of 16 tokens).  ``initial_state`` is used by
     rank 0; ``final_state`` (optional, any rank) receives the state after the last token.
@@ -87,6 +87,30 @@ def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bou
         assert q.shape[1] % 16 == 0, "every shard but the last must hold a multiple of 16 tokens"
     H, dev = q.shape[2], q.device
     payload = torch.zeros(2, 1, H, D, D, dtype=torch.float32, device=dev)
+    if parts > 1:
+        # every rank also splits its own shard into `parts` pieces (SequenceSplit): all ranks compute their
+        # composed map in parallel, exchange, fold, and finish from their true initial state
+        split = SequenceSplit(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, parts)
+        if world > 1:
+            Mt, Nt = split.maps()
+            payload[0].copy_(Mt)
+            payload[1].copy_(Nt)
+            gathered = [torch.empty_like(payload) for _ in range(world)]
+            dist.all_gather(gathered, payload, group=group)
+            S_in = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev) if initial_state is None \
+                else initial_state.to(torch.float32)
+            for j in range(rank):
+                S_in = torch.matmul(S_in, gathered[j][0]) + gathered[j][1]
+        else:
+            S_in = initial_state
+        end = split.finish(S_in, None)
+        if final_state is not None:
+            buf = end.contiguous() if rank == world - 1 else torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
+            if world > 1:
+                dist.broadcast(buf, src=dist.get_global_rank(group, world - 1) if group is not None else world - 1,
+                               group=group)
+            final_state.copy_(buf.to(final_state.dtype))
+        return
     if world == 1:
         fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, final_state, None)
         return
@@ -138,3 +162,75 @@ def fwd_sharded_emulated(n_shards: int, q, k, v, g, beta, scale, out, A_log, dt_
     out.copy_(torch.cat(outs, dim=1))
     if final_state is not None:
         final_state.copy_(last.to(final_state.dtype))
+
+
+class SequenceSplit:
+    """One long sequence on ONE GPU, split into ``parts`` contiguous pieces that run side by side.
+
+    A single (sequence, head) chain is serial, so a lone long sequence keeps only H of the GPU's
+    hundreds of chain slots busy.  The same map-and-fold scheme as for context parallelism fixes that
+    without any communication: view ``[1, T, H, 128]`` as a batch ``[parts, T/parts, H, 128]`` (no
+    copy), compute every piece's ``(M, N)`` in two batched calls (``maps``), fold the pieces in order
+    and run the batch once more from the true initial states (``finish``).  The prepare stage runs
+    once: its records do not depend on v or on the state, so the second and third call reuse the
+    workspace (``phase_mask``).  Results agree with the one-shot run to the parity tolerances (piece
+    boundaries carry the kernel's bf16 roundings), not bit for bit.  T must be a multiple of 16 * parts.
+    """
+
+    def __init__(self, q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, parts: int):
+        import flashkda_b200 as F
+        B, T, H, _ = q.shape
+        assert B == 1 and T % (16 * parts) == 0, "T must be a multiple of 16 * parts"
+        self.F, self.P, self.H, self.dev = F, parts, H, q.device
+        vw = lambda x: x.view(parts, T // parts, *x.shape[2:])
+        self.t = (vw(q), vw(k), vw(v), vw(g), vw(beta))
+        self.out = vw(out)
+        self.args = (A_log, dt_bias, lower_bound)
+        self.scale = scale
+        self.ws = torch.empty(max(1, F.get_workspace_size(T, H, parts)), dtype=torch.uint8, device=self.dev)
+        self.M = self.N = None
+
+    def maps(self):
+        """Per-piece maps (kept) and the composed map of the whole sequence ``(M_total, N_total)``."""
+        from . import _lib
+        P, H, dev = self.P, self.H, self.dev
+        qb, kb, vb, gb, bb = self.t
+        self.N = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
+        self.M = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
+        eye = torch.eye(D, dtype=torch.float32, device=dev).expand(P, H, D, D).contiguous()
+        # pass 1a: prepare + recurrence from zero (N);  pass 1b: recurrence only, v = 0 from the identity (M)
+        self.F.fwd(qb, kb, vb, gb, bb, self.scale, self.out, *self.args, None, self.N, None, workspace=self.ws)
+        self.F.fwd(qb, kb, torch.zeros_like(vb), gb, bb, self.scale, self.out, *self.args, eye, self.M, None,
+                   workspace=self.ws, phase_mask=_lib.PHASE_RECURRENCE)
+        Mt, Nt = self.M[0:1], self.N[0:1]
+        for p in range(1, P):
+            Nt = torch.matmul(Nt, self.M[p:p + 1]) + self.N[p:p + 1]
+            Mt = torch.matmul(Mt, self.M[p:p + 1])
+        return Mt, Nt
+
+    def finish(self, initial_state=None, final_state=None):
+        """Fold the pieces from ``initial_state`` and run the batch for real (writes ``out``)."""
+        from . import _lib
+        if self.M is None:
+            self.maps()
+        P, H, dev = self.P, self.H, self.dev
+        qb, kb, vb, gb, bb = self.t
+        S = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev) if initial_state is None \
+            else initial_state.to(torch.float32)
+        h0 = torch.empty(P, H, D, D, dtype=torch.float32, device=dev)
+        for p in range(P):
+            h0[p] = S[0]
+            if p + 1 < P:
+                S = torch.matmul(S, self.M[p:p + 1]) + self.N[p:p + 1]
+        hT = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
+        self.F.fwd(qb, kb, vb, gb, bb, self.scale, self.out, *self.args, h0, hT, None, workspace=self.ws,
+                   phase_mask=_lib.PHASE_RECURRENCE)
+        if final_state is not None:
+            final_state.copy_(hT[P - 1:P].to(final_state.dtype))
+        return hT[P - 1:P]
+
+
+def fwd_sequence_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None,
+                          final_state=None, parts: int = 8):
+    """Single-GPU forward of one long sequence split into ``parts`` pieces (see ``SequenceSplit``)."""
+    SequenceSplit(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, parts).finish(initial_state, final_state)

@@ -109,3 +109,21 @@ def test_emulated_shards_match_one_shot_gpu(shards):
     assert oracle.max_abs(one_out, out) <= 2e-2
     assert oracle.err_ratio(one_out, out) <= 1e-2
     assert oracle.err_ratio(one_hT, hT) <= 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("parts", [2, 8])
+def test_sequence_parallel_single_gpu(parts):
+    import flashkda_b200
+    inp = to_device(_weak_decay_inputs(4096, 4, 23), "cuda")
+    one_out, one_hT = torch.zeros_like(inp["out"]), torch.zeros_like(inp["final_state"])
+    flashkda_b200.fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], one_out, inp["A_log"],
+                      inp["dt_bias"], inp["lower_bound"], inp["initial_state"], one_hT)
+    out, hT = torch.zeros_like(one_out), torch.zeros_like(one_hT)
+    cp.fwd_sequence_parallel(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], out, inp["A_log"],
+                             inp["dt_bias"], inp["lower_bound"], inp["initial_state"], hT, parts=parts)
+    torch.cuda.synchronize()
+    print(f"parts {parts}: out ratio {oracle.err_ratio(one_out, out):.3e} state ratio {oracle.err_ratio(one_hT, hT):.3e}")
+    assert oracle.max_abs(one_out, out) <= 2e-2
+    assert oracle.err_ratio(one_out, out) <= 1e-2
+    assert oracle.err_ratio(one_hT, hT) <= 1e-2
