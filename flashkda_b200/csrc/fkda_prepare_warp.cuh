@@ -14,7 +14,7 @@
 
 namespace fkda {
 
-constexpr int kPwLd16 = 24;   // fp16 row pitch of the 16x16 matrices
+constexpr int kPwLd16 = 20;   // fp16 row pitch of the 16x16 matrices
 constexpr int kPwKiLbo = 272;  // ki tile: K-major core matrices, 16-byte K chunks 272 bytes apart (256 + 16 padding)
 
 // Per-warp shared memory.  b1 is the B1 part of the record ([kd; qd] in its final UMMA layout, see
@@ -252,7 +252,7 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
 
 // Grid-stride kernel: warp w of the grid takes (chunk, head) pairs w, w + W, ... with the head index
 // fastest, so that neighbouring warps read neighbouring 256-byte rows.
-constexpr int kPwWarpsPerCta = 15;
+constexpr int kPwWarpsPerCta = 16;
 template <bool kTc>
 __global__ void __launch_bounds__(kPwWarpsPerCta * 32, 1) prepare_warp_kernel(const __grid_constant__ TwoPassArgs a) {
     extern __shared__ __align__(16) uint8_t pw_smem[];

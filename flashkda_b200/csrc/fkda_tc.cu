@@ -20,6 +20,7 @@
 // Numerics: steps B1-B7 of the reference's contract (tests/torch_ref.py:231-251; the reference's own
 // recurrence is csrc/smxx/fwd_kernel2.cuh:434-742, built on mma.sync with register transposes).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
@@ -479,10 +480,22 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 // with fewer chains every chain has its own slot and whole chains are the work items.
 constexpr int64_t kSegThresholdChains = 384;
 constexpr int kSegChunks = 64;  // even, so that the double-buffer parity of a segment's first chunk is fixed
+// tuning aid: $FKDA_SEG_CHUNKS overrides the segment length (read once per process)
+static int seg_chunks_setting() {
+    static int v = 0;
+    if (v == 0) {
+        v = kSegChunks;
+        if (const char* e = getenv("FKDA_SEG_CHUNKS")) {
+            const int x = atoi(e) / 2 * 2;
+            if (x >= 2) v = x;
+        }
+    }
+    return v;
+}
 static bool use_segments(int64_t H, int64_t N) { return H * N > kSegThresholdChains; }
 static size_t seg_slot_count(int64_t T_total, int64_t H, int64_t N) {
     // one push per segment after the first of each chain, plus one ticket per resident warpgroup at the end
-    return (size_t)(H * (ws_tiles_upper_bound(T_total, N) / kSegChunks + N) + 4096);
+    return (size_t)(H * (ws_tiles_upper_bound(T_total, N) / seg_chunks_setting() + N) + 4096);
 }
 static size_t seg_slots_bytes(int64_t T_total, int64_t H, int64_t N) {
     return use_segments(H, N) ? (seg_slot_count(T_total, H, N) * 4 + 255) / 256 * 256 : 0;
@@ -538,7 +551,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         if (use_segments(p.H, p.N)) {
             a.qslots = reinterpret_cast<int32_t*>(base);
             a.seg_state = reinterpret_cast<uint32_t*>(base + slots);
-            a.seg_chunks = kSegChunks;
+            a.seg_chunks = seg_chunks_setting();
             if (do_rec && cudaMemsetAsync(a.qslots, 0xff, slots, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;
         }
         a.workspace = base + slots + states;
