@@ -126,6 +126,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
     uint32_t full_phase[kTcStages] = {0, 0};
     uint32_t mma_phase = 0;
     bool failed = false;
+    bool first_ticket = true;
 #ifdef FKDA_TC_TIMING
     long long stamps[24] = {0};
 #endif
@@ -137,7 +138,10 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
         //      take turns on the chain slots (first come, first served) and more chains than slots still
         //      share the machine evenly.  A waiter leaves when all chains are finished. ----
         if (v == 0) {
-            const int ticket = atomicAdd(a.queue, 1);
+            // first ticket of a chain slot: static, chain slots of all CTAs filled one layer at a time (so that
+            // few chains spread over the SMs instead of crowding the first CTAs); later tickets: first come
+            const int ticket = first_ticket ? wg * (int)gridDim.x + (int)blockIdx.x
+                                            : kTcChains * (int)gridDim.x + atomicAdd(a.queue, 1);
             int item = -2;  // -2: no more work, -3: gave up waiting
             if (ticket < n_chains) {
                 item = ticket;
@@ -157,6 +161,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             }
             ctl.next_chain[wg] = item;
         }
+        first_ticket = false;
         named_barrier_sync(bar_id, 128);
         const int item = ctl.next_chain[wg];
         if (item == -3) { failed = true; break; }
@@ -573,7 +578,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
             cudaSuccess)
             return FKDA_ERR_LAUNCH;
         const int64_t chains = p.N * p.H;
-        int64_t ctas = (chains + kTcChains - 1) / kTcChains;
+        int64_t ctas = chains;  // one chain per SM while they last, then two, then three
         if (ctas > sms) ctas = sms;
         if (ctas < 1) ctas = 1;
         TcMaps maps;
