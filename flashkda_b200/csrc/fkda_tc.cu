@@ -480,6 +480,12 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
     }
 }
 
+}  // namespace fkda
+
+#include "fkda_tc_wide.cuh"
+
+namespace fkda {
+
 // ---------------------------------------------------------------------------------
 // Segment scheduling is used when there are more chains than a B200 can hold at once (3 per SM);
 // with fewer chains every chain has its own slot and whole chains are the work items.
@@ -585,7 +591,17 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         if (!encode_token_map(&maps.v, p.v, p.B * p.T, p.H, p.token_stride) ||
             !encode_token_map(&maps.out, p.out, p.B * p.T, p.H, p.token_stride))
             return FKDA_ERR_LAUNCH;
-        recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a, maps);
+        static const bool no_wide = getenv("FKDA_TC_NO_WIDE") != nullptr;  // tuning aid
+        if (chains <= sms && !no_wide) {
+            // few chains: one per CTA, the idle warpgroups help with the state update
+            const int wide_smem = kSmChainBytes + (int)sizeof(TcWideCtrl) + 128;
+            if (cudaFuncSetAttribute(recurrence_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem) !=
+                cudaSuccess)
+                return FKDA_ERR_LAUNCH;
+            recurrence_tc_wide_kernel<<<(unsigned)ctas, 384, wide_smem, stream>>>(a, maps);
+        } else {
+            recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a, maps);
+        }
         ++launches;
     }
     if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
