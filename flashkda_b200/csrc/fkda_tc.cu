@@ -483,6 +483,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 }  // namespace fkda
 
 #include "fkda_tc_wide.cuh"
+#include "fkda_tc_ts.cuh"
 
 namespace fkda {
 
@@ -591,7 +592,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         if (!encode_token_map(&maps.v, p.v, p.B * p.T, p.H, p.token_stride) ||
             !encode_token_map(&maps.out, p.out, p.B * p.T, p.H, p.token_stride))
             return FKDA_ERR_LAUNCH;
-        static const bool no_wide = getenv("FKDA_TC_NO_WIDE") != nullptr;  // tuning aid
+        const bool no_wide = getenv("FKDA_TC_NO_WIDE") != nullptr;  // tuning aid
         if (chains <= sms && !no_wide) {
             // few chains: one per CTA, the idle warpgroups help with the state update
             const int wide_smem = kSmChainBytes + (int)sizeof(TcWideCtrl) + 128;
@@ -599,8 +600,14 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
                 cudaSuccess)
                 return FKDA_ERR_LAUNCH;
             recurrence_tc_wide_kernel<<<(unsigned)ctas, 384, wide_smem, stream>>>(a, maps);
-        } else {
+        } else if (getenv("FKDA_TC_TS") == nullptr) {
             recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a, maps);
+        } else {
+            // opt-in variant with the state's MMA copy in tensor memory (same speed, 98 KB less shared memory)
+            if (cudaFuncSetAttribute(recurrence_tc_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmemBytes) !=
+                cudaSuccess)
+                return FKDA_ERR_LAUNCH;
+            recurrence_tc_ts_kernel<<<(unsigned)ctas, kTcChains * 128, kTsSmemBytes, stream>>>(a, maps);
         }
         ++launches;
     }
