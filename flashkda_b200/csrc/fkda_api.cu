@@ -1,5 +1,7 @@
 // C ABI of the library: argument validation and dispatch to the device implementations.
 // Replaces the reference's host binding (csrc/flash_kda.cpp:28-217) below its tensor checks.
+#include <stdlib.h>
+
 #include "fkda_internal.h"
 
 namespace {
@@ -79,8 +81,13 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
         return FKDA_ERR_WORKSPACE;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     int launches = 0;
-    int rc = (algo == FKDA_ALGO_TC) ? fkda::launch_tc(*p, stream, &launches)
-                                    : fkda::launch_twopass(*p, stream, &launches);
+    int rc;
+    if (algo == FKDA_ALGO_TC && fkda::decode_eligible(*p) && getenv("FKDA_NO_DECODE") == nullptr)
+        rc = fkda::launch_decode(*p, stream, &launches);  // one token per sequence: state read-modify-write
+    else if (algo == FKDA_ALGO_TC)
+        rc = fkda::launch_tc(*p, stream, &launches);
+    else
+        rc = fkda::launch_twopass(*p, stream, &launches);
     if (rc == FKDA_OK) g_last_launches = launches;
     return rc;
 }

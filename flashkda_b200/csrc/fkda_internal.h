@@ -44,6 +44,9 @@ size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
 int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
 size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
 int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
+// Decode step (fixed batch, T == 1): one read-modify-write kernel over the states, no workspace records.
+bool decode_eligible(const fkda_fwd_params& p);
+int launch_decode(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
 
 // Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
 // workspace carving).
