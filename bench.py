@@ -271,7 +271,13 @@ def run_ours(a):
     kernel_times = {}
     n_phase = 3
     barrier()
-    if not cp_mode and a.seq_parts == 1:
+    decode = (w_local.T == 1 and inp.get("cu_seqlens") is None and algo != "twopass"
+              and not os.environ.get("FKDA_NO_DECODE"))
+    if decode and not cp_mode and a.seq_parts == 1:
+        # one token per sequence: the library runs its single decode kernel (no phases to time apart)
+        kernel_name, kernel_ms = "fkda::decode_kernel", ms_step
+        kernel_times[kernel_name] = ms_step
+    elif not cp_mode and a.seq_parts == 1:
         step()
         for name, mask in zip(names, (_lib.PHASE_PREPARE, _lib.PHASE_RECURRENCE)):
             p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -313,9 +319,11 @@ def run_ours(a):
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
-        per_unit = json.load(open(tpath)).get(kernel_name, {}).get("bytes_per_unit")
-        if per_unit is not None:  # scaled from the small ncu capture by the (chunk, head) units of this launch
-            traffic = per_unit * ((w_local.tokens + 15) // 16) * w.H
+        entry = json.load(open(tpath)).get(kernel_name, {})
+        if entry.get("bytes_per_unit") is not None:  # scaled from the small ncu capture by the (chunk, head) units
+            traffic = entry["bytes_per_unit"] * ((w_local.tokens + 15) // 16) * w.H
+        elif entry.get("traffic_over_algorithmic") is not None:  # state-bound kernels: scaled by the algorithmic bytes
+            traffic = entry["traffic_over_algorithmic"] * alg_bytes
 
     cpu = None
     if not a.no_cpu and world == 1:
