@@ -74,14 +74,43 @@ __device__ __forceinline__ float row_sumsq(const float (&x)[4], int lane) {
     return __shfl_sync(0xffffffffu, c, lane | 1);                 // the odd lanes hold the group sums
 }
 
+// What a warp fetches ahead of a chunk: the first kPf rows of q, k, g (my 4 columns), and the per-chunk
+// scalars.  Filled for the NEXT unit while the current one is in its last (memory-free) stage, so that a
+// chunk does not start with an exposed DRAM round trip.
+constexpr int kPf = 4;  // rows fetched ahead of their use
+struct PrepPrefetch {
+    uint2 q[kPf], k[kPf], g[kPf];
+    float4 dtv;
+    float a_log, beta_logit;  // beta of row `lane` (lanes below 16; 0 past the end, as zero padding does)
+};
+__device__ __forceinline__ void prep_prefetch(const TwoPassArgs& a, int64_t t0, int len, int h, int lane,
+                                              PrepPrefetch& p) {
+    const int c4 = lane * 4;
+    const int64_t base = t0 * a.token_stride + (int64_t)h * kD + c4;
+#pragma unroll
+    for (int r = 0; r < kPf; ++r) {
+        p.q[r] = p.k[r] = p.g[r] = make_uint2(0, 0);
+        if (r < len) {
+            p.q[r] = __ldg(reinterpret_cast<const uint2*>(a.q + base + (int64_t)r * a.token_stride));
+            p.k[r] = __ldg(reinterpret_cast<const uint2*>(a.k + base + (int64_t)r * a.token_stride));
+            p.g[r] = __ldg(reinterpret_cast<const uint2*>(a.g + base + (int64_t)r * a.token_stride));
+        }
+    }
+    p.dtv = __ldg(reinterpret_cast<const float4*>(a.dt_bias + (int64_t)h * kD + c4));
+    p.a_log = __ldg(a.A_log + h);
+    p.beta_logit = 0.0f;
+    if (lane < len) p.beta_logit = bf2f(a.beta[(t0 + lane) * a.beta_token_stride + h]);  // len <= 16
+}
+
 // One warp, one (chunk, head).  `ws` is the record to fill; kTc selects its layout (see fkda_common.cuh).
+// `pf` holds the prefetched head of this chunk and leaves holding that of the next unit (if `next_valid`).
 template <bool kTc>
 __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t t0, int len, int h, uint8_t* ws,
-                                                   PrepWarpSmem& sm, int lane) {
+                                                   PrepWarpSmem& sm, int lane, PrepPrefetch& pf, bool next_valid,
+                                                   int64_t next_t0, int next_len, int next_h) {
     const int c4 = lane * 4;  // my 4 columns
-    const float a_exp = ex2_approx(__fmul_rn(a.A_log[h], 1.4426950408889634f));
-    const float4 dtv = *reinterpret_cast<const float4*>(a.dt_bias + (int64_t)h * kD + c4);
-    const float dt[4] = {dtv.x, dtv.y, dtv.z, dtv.w};
+    const float a_exp_half = __fmul_rn(ex2_approx(__fmul_rn(pf.a_log, 1.4426950408889634f)), 0.5f);
+    const float dt[4] = {pf.dtv.x, pf.dtv.y, pf.dtv.z, pf.dtv.w};
     const uint32_t sc2 = pack_bf2(a.scale, a.scale);
     const __nv_bfloat16* qp = a.q + t0 * a.token_stride + (int64_t)h * kD + c4;
     const __nv_bfloat16* kp = a.k + t0 * a.token_stride + (int64_t)h * kD + c4;
@@ -89,17 +118,14 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
 
     // sigmoid(beta) of row `lane` (rows past the end use logit 0, as zero padding does)
     if (lane < kChunk) {
-        float b = 0.0f;
-        if (lane < len) b = bf2f(a.beta[(t0 + lane) * a.beta_token_stride + h]);
-        const float sb = sigmoid_tanh(b);
+        const float sb = sigmoid_tanh(pf.beta_logit);
         sm.beta_act[lane] = sb;
         if constexpr (kTc) reinterpret_cast<float*>(ws + kTcBeta)[lane] = bf2f(f2bf(sb));
     }
 
     float csum[4] = {0.f, 0.f, 0.f, 0.f};  // running in-chunk gate sum of my columns
     // rows are fetched kPf rows ahead of their use so that several DRAM round trips overlap
-    constexpr int kPf = 4;
-    uint2 ring_q[kPf], ring_k[kPf], ring_g[kPf];
+    uint2 (&ring_q)[kPf] = pf.q, (&ring_k)[kPf] = pf.k, (&ring_g)[kPf] = pf.g;
     auto fetch = [&](int r, int slot) {
         ring_q[slot] = ring_k[slot] = ring_g[slot] = make_uint2(0, 0);
         if (r < len) {
@@ -108,8 +134,6 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
             ring_g[slot] = __ldg(reinterpret_cast<const uint2*>(gp + (int64_t)r * a.token_stride));
         }
     };
-#pragma unroll
-    for (int r = 0; r < kPf; ++r) fetch(r, r);
 #pragma unroll 1
     for (int rb = 0; rb < kChunk; rb += kPf) {
 #pragma unroll
@@ -131,8 +155,9 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         // gate = gate_scale * sigmoid(exp(A_log) * (g + dt_bias)), 0 past the end; cumulative over rows
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float x = __fmul_rn(a_exp, __fadd_rn(gv[i], dt[i]));
-            const float gt = valid ? __fmul_rn(a.gate_scale, sigmoid_tanh(x)) : 0.0f;
+            // sigmoid(x) = tanh(x/2)/2 + 1/2 with x = a_exp (g + dt): the halving is exact, so it is folded into a_exp
+            const float th = tanh_approx(__fmul_rn(a_exp_half, __fadd_rn(gv[i], dt[i])));
+            const float gt = valid ? __fmul_rn(a.gate_scale, __fmaf_rn(th, 0.5f, 0.5f)) : 0.0f;
             csum[i] = __fadd_rn(csum[i], gt);
         }
         // decay application in bf16x2: one rounding per element and operation
@@ -161,6 +186,8 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
     for (int i = 0; i < 4; ++i) et[i] = ex2_approx(csum[i]);
     *reinterpret_cast<float4*>(ws + (kTc ? kTcEt : kWsEt) + c4 * 4) = make_float4(et[0], et[1], et[2], et[3]);
     __syncwarp();
+    // the head of the next unit travels while the in-chunk products and the inverse (no global loads) run
+    if (next_valid) prep_prefetch(a, next_t0, next_len, next_h, lane, pf);
 
     // ---- L = fp16(kd ki^T) masked * fp16(beta), Mqk = bf16(qd ki^T) masked: mma.sync m16n8k16
     //      bf16 -> fp32, operand fragments fetched with conflict-free 32-bit loads ----
@@ -260,14 +287,27 @@ __global__ void __launch_bounds__(kPwWarpsPerCta * 32, 1) prepare_warp_kernel(co
     PrepWarpSmem& sm = reinterpret_cast<PrepWarpSmem*>(pw_smem)[warp];
     const int64_t n_units = a.total_tiles * a.H;
     const int64_t stride = (int64_t)gridDim.x * kPwWarpsPerCta;
-    for (int64_t u = (int64_t)blockIdx.x * kPwWarpsPerCta + warp; u < n_units; u += stride) {
+    // units past the last chunk of a ragged batch (upper-bound tile count) all sit at the end of the range
+    auto locate = [&](int64_t u, int64_t* t0, int* len, int* h) {
+        if (u >= n_units) return false;
         const int64_t tile = u / a.H;
-        const int h = (int)(u - tile * a.H);
-        int64_t t0;
-        int len;
-        if (!locate_tile(a, tile, &t0, &len)) continue;
+        *h = (int)(u - tile * a.H);
+        return locate_tile(a, tile, t0, len);
+    };
+    int64_t u = (int64_t)blockIdx.x * kPwWarpsPerCta + warp;
+    int64_t t0 = 0, t0n = 0;
+    int len = 0, h = 0, lenn = 0, hn = 0;
+    bool valid = locate(u, &t0, &len, &h);
+    PrepPrefetch pf;
+    if (valid) prep_prefetch(a, t0, len, h, lane, pf);
+    while (valid) {
+        const bool next_valid = locate(u + stride, &t0n, &lenn, &hn);
+        const int64_t tile = u / a.H;
         uint8_t* ws = a.workspace + ((int64_t)h * a.total_tiles + tile) * (int64_t)(kTc ? kTcRecord : kWsRecord);
-        prepare_chunk_warp<kTc>(a, t0, len, h, ws, sm, lane);
+        prepare_chunk_warp<kTc>(a, t0, len, h, ws, sm, lane, pf, next_valid, t0n, lenn, hn);
+        u += stride;
+        valid = next_valid;
+        t0 = t0n; len = lenn; h = hn;
     }
     sm100::bulk_wait_group<0>();  // (lane 0) the last records have landed
 }
