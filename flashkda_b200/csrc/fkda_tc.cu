@@ -47,7 +47,7 @@ constexpr uint32_t kTcWaitNs = 2000000000u;
 // byte offsets inside one chain's shared-memory block
 constexpr int kSmS = 0;                                    // S^T tile: the state as MN-major A operand [v, k]
 constexpr int kSmStage = 32768;                            // kTcStages chunk records
-constexpr int kSmStageBytes = kTcRecord;                   // 13888
+constexpr int kSmStageBytes = kTcRecord;                   // 14656
 constexpr int kSmV = kSmStage + kTcStages * kSmStageBytes;    // kTcStages value tiles [16][128] bf16 (60544)
 constexpr int kSmA23 = kSmV + kTcStages * 4096;               // A operand of the 16-deep products [128, 16]
 constexpr int kSmOut = kSmA23;                                // out tile [16][128] bf16: reuses the A23 tile, which
@@ -74,6 +74,141 @@ __device__ __forceinline__ int sT_off(int k, int vg) { return (k >> 3) * 2048 + 
 struct alignas(64) TcMaps {
     CUtensorMap v, out;
 };
+
+// ---------------------------------------------------------------------------------
+// Pieces shared by the recurrence kernels of this file and of fkda_tc_wide.cuh / fkda_tc_ts.cuh.
+
+// Where the tokens and records of one (sequence, head) chain live.
+struct TcChain {
+    int64_t n;        // sequence
+    int h;            // head
+    int64_t bos;      // first token
+    int64_t seq_len;
+    int n_chunks;
+    const uint8_t* rec_base;  // record of the chain's chunk 0
+};
+__device__ __forceinline__ TcChain tc_locate_chain(const TwoPassArgs& a, int64_t chain) {
+    TcChain c;
+    c.n = chain / a.H;
+    c.h = (int)(chain - c.n * a.H);
+    int64_t tile_base;
+    if (a.cu_seqlens != nullptr) {
+        c.bos = a.cu_seqlens[c.n];
+        c.seq_len = a.cu_seqlens[c.n + 1] - c.bos;
+        if (c.seq_len < 0) c.seq_len = 0;
+        tile_base = a.tile_prefix[c.n];
+    } else {
+        c.bos = c.n * a.T;
+        c.seq_len = a.T;
+        tile_base = c.n * ((a.T + kChunk - 1) / kChunk);
+    }
+    c.n_chunks = (int)((c.seq_len + kChunk - 1) / kChunk);
+    c.rec_base = a.workspace + ((int64_t)c.h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
+    return c;
+}
+
+// Next work item of a chain slot (called by ONE thread).  An item is one segment (seg_chunks chunks) of one
+// chain; item id = seg * n_chains + chain.  Tickets below n_chains are the first segments; every later ticket
+// reads the slot that the finisher of some segment fills with the follow-up segment, so chains take turns on
+// the chain slots (first come, first served) and more chains than slots still share the machine evenly.
+// The first ticket of a chain slot is static, the chain slots of all CTAs filled one layer at a time (so that
+// few chains spread over the SMs instead of crowding the first CTAs); later tickets are first come.
+// Returns the item, -2 when all chains are finished, -3 when the bounded wait gave up.
+__device__ __forceinline__ int tc_next_item(const TwoPassArgs& a, bool first_ticket, int wg, int64_t n_chains,
+                                            volatile int* abort_flag) {
+    const int ticket = first_ticket ? wg * (int)gridDim.x + (int)blockIdx.x
+                                    : kTcChains * (int)gridDim.x + atomicAdd(a.queue, 1);
+    if (ticket < n_chains) return ticket;
+    int item = -2;
+    if (a.seg_chunks > 0) {
+        volatile int32_t* slot = a.qslots + (ticket - (int)n_chains);
+        volatile int32_t* finished = a.queue + 3;
+        const uint64_t t0 = global_timer_ns();
+        uint32_t spins = 0;
+        for (;;) {
+            const int x = *slot;
+            if (x >= 0) { item = x; break; }
+            if (*finished >= (int)n_chains) break;
+            if ((++spins & 63u) == 0 && (*abort_flag != 0 || global_timer_ns() - t0 > kTcWaitNs)) { item = -3; break; }
+            __nanosleep(200);
+        }
+        __threadfence();  // the pusher's state stores are visible before we read them
+    }
+    return item;
+}
+// The finisher of a non-final segment queues the follow-up segment (ONE thread, after the state hand-over
+// stores of all threads have been fenced and a barrier has passed).
+__device__ __forceinline__ void tc_push_followup(const TwoPassArgs& a, int item, int64_t n_chains) {
+    const int pos = atomicAdd(a.queue + 2, 1);
+    __threadfence();
+    *reinterpret_cast<volatile int32_t*>(a.qslots + pos) = item + (int)n_chains;
+}
+
+// sigmoid(beta) of the 16 rows as bf16x2 pairs (the record holds bf16-rounded fp32 values)
+__device__ __forceinline__ void tc_load_beta(const uint8_t* rec, uint32_t (&bpk)[8]) {
+    const float4* bp = reinterpret_cast<const float4*>(rec + kTcBeta);
+#pragma unroll
+    for (int i4 = 0; i4 < 4; ++i4) {
+        const float4 b = bp[i4];
+        bpk[2 * i4] = pack_bf2(b.x, b.y);
+        bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
+    }
+}
+// value column v of the chunk from the [16][128] tile (zero past the sequence end)
+__device__ __forceinline__ void tc_load_v_column(const uint8_t* v_tile, int v, int len, unsigned short (&v_cur)[kChunk]) {
+    const unsigned short* vt = reinterpret_cast<const unsigned short*>(v_tile) + v;
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
+}
+// Row v of a [128, 16] K-major operand tile (the A operand of the 16-deep products): two 16-byte pieces.
+__device__ __forceinline__ void tc_store_a23_row(uint8_t* a23, int v, const uint32_t (&p)[8]) {
+    uint8_t* ap = a23 + (v >> 3) * 128 + (v & 7) * 16;
+    *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
+    *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
+}
+// u' = (v (-) bf(u0)) (*) bf(beta) for V row v, from the u0 accumulators in tensor memory, into the A tile
+__device__ __forceinline__ void tc_form_u_prime(uint32_t t_u0_lane, uint8_t* a23, int v,
+                                                const unsigned short (&v_cur)[kChunk], const uint32_t (&bpk)[8]) {
+    uint32_t r[16];
+    tmem_ld16(t_u0_lane, r);
+    tmem_wait_ld();
+    uint32_t up[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
+        up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
+    }
+    tc_store_a23_row(a23, v, up);
+}
+// U = bf(D2) for V row v into the A tile
+__device__ __forceinline__ void tc_form_u(uint32_t t_d2_lane, uint8_t* a23, int v) {
+    uint32_t r[16];
+    tmem_ld16(t_d2_lane, r);
+    tmem_wait_ld();
+    uint32_t p[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    tc_store_a23_row(a23, v, p);
+}
+// out = bf(o0) (+) bf(Mqk U) for V row v; r holds D3 in 0-15 and o0 in 16-31.  Full chunks go through the out
+// tile (one TMA store later), ragged tails straight to global memory, valid rows only.
+__device__ __forceinline__ void tc_store_out(const uint32_t (&r)[32], unsigned short* out_tile, unsigned short* out_global,
+                                             int64_t tstride, int v, int len) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t o = bf2_add(pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1])),
+                                   pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
+        if (len == kChunk) {
+            out_tile[(2 * i) * kD + v] = (unsigned short)(o & 0xffffu);
+            out_tile[(2 * i + 1) * kD + v] = (unsigned short)(o >> 16);
+        } else {
+            unsigned short* dst = out_global + (int64_t)(2 * i) * tstride;
+            if (2 * i < len) dst[0] = (unsigned short)(o & 0xffffu);
+            if (2 * i + 1 < len) dst[tstride] = (unsigned short)(o >> 16);
+        }
+    }
+}
 
 __global__ void __launch_bounds__(kTcChains * 128, 1)
 recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constant__ TcMaps maps) {
@@ -132,35 +267,8 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 #endif
 
     while (!failed) {
-        // ---- next work item.  An item is one segment (seg_chunks chunks) of one chain; item id =
-        //      seg * n_chains + chain.  Tickets below n_chains are the first segments; every later ticket
-        //      reads the slot that the finisher of some segment fills with the follow-up segment, so chains
-        //      take turns on the chain slots (first come, first served) and more chains than slots still
-        //      share the machine evenly.  A waiter leaves when all chains are finished. ----
-        if (v == 0) {
-            // first ticket of a chain slot: static, chain slots of all CTAs filled one layer at a time (so that
-            // few chains spread over the SMs instead of crowding the first CTAs); later tickets: first come
-            const int ticket = first_ticket ? wg * (int)gridDim.x + (int)blockIdx.x
-                                            : kTcChains * (int)gridDim.x + atomicAdd(a.queue, 1);
-            int item = -2;  // -2: no more work, -3: gave up waiting
-            if (ticket < n_chains) {
-                item = ticket;
-            } else if (a.seg_chunks > 0) {
-                volatile int32_t* slot = a.qslots + (ticket - (int)n_chains);
-                volatile int32_t* finished = a.queue + 3;
-                const uint64_t t0 = global_timer_ns();
-                uint32_t spins = 0;
-                for (;;) {
-                    const int x = *slot;
-                    if (x >= 0) { item = x; break; }
-                    if (*finished >= (int)n_chains) break;
-                    if ((++spins & 63u) == 0 && (*abort_flag != 0 || global_timer_ns() - t0 > kTcWaitNs)) { item = -3; break; }
-                    __nanosleep(200);
-                }
-                __threadfence();  // the pusher's state stores are visible before we read them
-            }
-            ctl.next_chain[wg] = item;
-        }
+        // ---- next work item (a segment of a chain) ----
+        if (v == 0) ctl.next_chain[wg] = tc_next_item(a, first_ticket, wg, n_chains, abort_flag);
         first_ticket = false;
         named_barrier_sync(bar_id, 128);
         const int item = ctl.next_chain[wg];
@@ -168,23 +276,12 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
         if (item < 0) break;
         const int seg = item / (int)n_chains;
         const int64_t chain = item - (int64_t)seg * n_chains;
-        const int64_t n = chain / a.H;
-        const int h = (int)(chain - n * a.H);
-        int64_t bos, seq_len, tile_base;
-        if (a.cu_seqlens != nullptr) {
-            bos = a.cu_seqlens[n];
-            seq_len = a.cu_seqlens[n + 1] - bos;
-            if (seq_len < 0) seq_len = 0;
-            tile_base = a.tile_prefix[n];
-        } else {
-            bos = n * a.T;
-            seq_len = a.T;
-            tile_base = n * ((a.T + kChunk - 1) / kChunk);
-        }
-        const int n_chunks = (int)((seq_len + kChunk - 1) / kChunk);
+        const TcChain ch = tc_locate_chain(a, chain);
+        const int64_t n = ch.n, bos = ch.bos, seq_len = ch.seq_len;
+        const int h = ch.h, n_chunks = ch.n_chunks;
         const int c0 = seg * a.seg_chunks;                                             // my chunk range
         const int c1 = (a.seg_chunks > 0 && c0 + a.seg_chunks < n_chunks) ? c0 + a.seg_chunks : n_chunks;
-        const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
+        const uint8_t* rec_base = ch.rec_base;
         // thread k = v owns state column k: element S[vv][k] of this chain sits at st_base + vv * 128
         const int64_t st_base = (n * a.H + h) * (int64_t)(kD * kD) + v;
 #ifdef FKDA_TC_TIMING
@@ -267,43 +364,17 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             // work off the critical path while the MMA runs
             const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk);
             unsigned short v_cur[kChunk];  // value column v of this chunk (zero past the sequence end)
-            {
-                const unsigned short* vt = reinterpret_cast<const unsigned short*>(cs + kSmV + s * 4096) + v;
-#pragma unroll
-                for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
-            }
+            tc_load_v_column(cs + kSmV + s * 4096, v, len, v_cur);
             const float e_mine = reinterpret_cast<const float*>(st + kTcEt)[v];  // gate decay of my state column
-            uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta) (the record holds bf16-rounded values)
-            {
-                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
-#pragma unroll
-                for (int i4 = 0; i4 < 4; ++i4) {
-                    const float4 b = bp[i4];
-                    bpk[2 * i4] = pack_bf2(b.x, b.y);
-                    bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
-                }
-            }
+            uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta)
+            tc_load_beta(st, bpk);
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(2);
 
             // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
-            {
-                uint32_t r[16];
-                tmem_ld16(t_d1 + lane_sel, r);
-                tmem_wait_ld();
-                uint32_t up[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
-                    up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
-                }
-                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                *reinterpret_cast<uint4*>(ap) = make_uint4(up[0], up[1], up[2], up[3]);
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(up[4], up[5], up[6], up[7]);
-            }
+            tc_form_u_prime(t_d1 + lane_sel, cs + kSmA23, v, v_cur, bpk);
             TC_STAMP(3);
             fence_proxy_async_smem();
             tc_fence_before_sync();
@@ -323,17 +394,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
             mma_phase ^= 1u;
             tc_fence_after_sync();
             TC_STAMP(5);
-            {
-                uint32_t r[16];
-                tmem_ld16(t_ds + lane_sel, r);
-                tmem_wait_ld();
-                uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                uint32_t p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
-            }
+            tc_form_u(t_ds + lane_sel, cs + kSmA23, v);  // U = bf(D2)
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
@@ -363,19 +424,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
                 tmem_ld16(t_ds + lane_sel, ra);
                 tmem_wait_ld();
                 tmem_ld16(t_ds + 16 + lane_sel, rb);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t o = bf2_add(pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1])),
-                                               pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
-                    if (len == kChunk) {  // full chunk: through the out tile and one TMA store
-                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i) * kD + v] = (unsigned short)(o & 0xffffu);
-                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i + 1) * kD + v] = (unsigned short)(o >> 16);
-                    } else {              // ragged tail: only the valid rows, straight to global memory
-                        unsigned short* dst = ocol + ((int64_t)t * kChunk + 2 * i) * tstride;
-                        if (2 * i < len) dst[0] = (unsigned short)(o & 0xffffu);
-                        if (2 * i + 1 < len) dst[tstride] = (unsigned short)(o >> 16);
-                    }
-                }
+                tc_store_out(r, reinterpret_cast<unsigned short*>(out_tile), ocol + (int64_t)t * kChunk * tstride, tstride, v, len);
             }
             // ---- state column k (thread = TMEM lane k of DST): S[vv][k] = bf(fma(S[vv][k], E_tot[k], DST[k][vv])),
             //      registers only; the refreshed column also goes to the S^T tile for the next chunk's MMA1 ----
@@ -437,11 +486,7 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
                 seg_mine[i * 128] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
             __threadfence();
             named_barrier_sync(bar_id, 128);
-            if (v == 0) {
-                const int pos = atomicAdd(a.queue + 2, 1);
-                __threadfence();
-                *reinterpret_cast<volatile int32_t*>(a.qslots + pos) = item + (int)n_chains;
-            }
+            if (v == 0) tc_push_followup(a, item, n_chains);
             continue;
         }
         if (v == 0) atomicAdd(a.queue + 3, 1);  // this chain is finished

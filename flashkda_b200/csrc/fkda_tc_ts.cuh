@@ -75,29 +75,8 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
     bool first_ticket = true;
 
     while (!failed) {
-        // ---- next work item (segment of a chain), as in recurrence_tc_kernel ----
-        if (v == 0) {
-            const int ticket = first_ticket ? wg * (int)gridDim.x + (int)blockIdx.x
-                                            : kTcChains * (int)gridDim.x + atomicAdd(a.queue, 1);
-            int item = -2;  // -2: no more work, -3: gave up waiting
-            if (ticket < n_chains) {
-                item = ticket;
-            } else if (a.seg_chunks > 0) {
-                volatile int32_t* slot = a.qslots + (ticket - (int)n_chains);
-                volatile int32_t* finished = a.queue + 3;
-                const uint64_t t0 = global_timer_ns();
-                uint32_t spins = 0;
-                for (;;) {
-                    const int x = *slot;
-                    if (x >= 0) { item = x; break; }
-                    if (*finished >= (int)n_chains) break;
-                    if ((++spins & 63u) == 0 && (*abort_flag != 0 || global_timer_ns() - t0 > kTcWaitNs)) { item = -3; break; }
-                    __nanosleep(200);
-                }
-                __threadfence();  // the pusher's state stores are visible before we read them
-            }
-            ctl.next_chain[wg] = item;
-        }
+        // ---- next work item (a segment of a chain) ----
+        if (v == 0) ctl.next_chain[wg] = tc_next_item(a, first_ticket, wg, n_chains, abort_flag);
         first_ticket = false;
         named_barrier_sync(bar_id, 128);
         const int item = ctl.next_chain[wg];
@@ -105,23 +84,12 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
         if (item < 0) break;
         const int seg = item / (int)n_chains;
         const int64_t chain = item - (int64_t)seg * n_chains;
-        const int64_t n = chain / a.H;
-        const int h = (int)(chain - n * a.H);
-        int64_t bos, seq_len, tile_base;
-        if (a.cu_seqlens != nullptr) {
-            bos = a.cu_seqlens[n];
-            seq_len = a.cu_seqlens[n + 1] - bos;
-            if (seq_len < 0) seq_len = 0;
-            tile_base = a.tile_prefix[n];
-        } else {
-            bos = n * a.T;
-            seq_len = a.T;
-            tile_base = n * ((a.T + kChunk - 1) / kChunk);
-        }
-        const int n_chunks = (int)((seq_len + kChunk - 1) / kChunk);
+        const TcChain ch = tc_locate_chain(a, chain);
+        const int64_t n = ch.n, bos = ch.bos, seq_len = ch.seq_len;
+        const int h = ch.h, n_chunks = ch.n_chunks;
         const int c0 = seg * a.seg_chunks;                                             // my chunk range
         const int c1 = (a.seg_chunks > 0 && c0 + a.seg_chunks < n_chunks) ? c0 + a.seg_chunks : n_chunks;
-        const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
+        const uint8_t* rec_base = ch.rec_base;
         // thread v owns state row v: element S[v][k] of this chain sits at st_base + k
         const int64_t st_base = ((n * a.H + h) * (int64_t)kD + v) * (int64_t)kD;
 
@@ -206,41 +174,15 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             // work off the critical path while the MMA runs
             const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk);
             unsigned short v_cur[kChunk];  // value column v of this chunk (zero past the sequence end)
-            {
-                const unsigned short* vt = reinterpret_cast<const unsigned short*>(cs + kTsV + s * 4096) + v;
-#pragma unroll
-                for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
-            }
-            uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta) (the record holds bf16-rounded values)
-            {
-                const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
-#pragma unroll
-                for (int i4 = 0; i4 < 4; ++i4) {
-                    const float4 b = bp[i4];
-                    bpk[2 * i4] = pack_bf2(b.x, b.y);
-                    bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
-                }
-            }
+            tc_load_v_column(cs + kTsV + s * 4096, v, len, v_cur);
+            uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta)
+            tc_load_beta(st, bpk);
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
 
             // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
-            {
-                uint32_t r[16];
-                tmem_ld16(t_d1 + lane_sel, r);
-                tmem_wait_ld();
-                uint32_t up[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
-                    up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
-                }
-                uint8_t* ap = cs + kTsA23 + (v >> 3) * 128 + (v & 7) * 16;
-                *reinterpret_cast<uint4*>(ap) = make_uint4(up[0], up[1], up[2], up[3]);
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(up[4], up[5], up[6], up[7]);
-            }
+            tc_form_u_prime(t_d1 + lane_sel, cs + kTsA23, v, v_cur, bpk);
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
@@ -257,17 +199,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
-            {
-                uint32_t r[16];
-                tmem_ld16(t_ds + lane_sel, r);
-                tmem_wait_ld();
-                uint8_t* ap = cs + kTsA23 + (v >> 3) * 128 + (v & 7) * 16;
-                uint32_t p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
-                *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
-            }
+            tc_form_u(t_ds + lane_sel, cs + kTsA23, v);  // U = bf(D2)
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
@@ -295,19 +227,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
                 tmem_ld16(t_ds + lane_sel, ra);
                 tmem_wait_ld();
                 tmem_ld16(t_ds + 16 + lane_sel, rb);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t o = bf2_add(pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1])),
-                                               pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
-                    if (len == kChunk) {  // full chunk: through the out tile and one TMA store
-                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i) * kD + v] = (unsigned short)(o & 0xffffu);
-                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i + 1) * kD + v] = (unsigned short)(o >> 16);
-                    } else {              // ragged tail: only the valid rows, straight to global memory
-                        unsigned short* dst = ocol + ((int64_t)t * kChunk + 2 * i) * tstride;
-                        if (2 * i < len) dst[0] = (unsigned short)(o & 0xffffu);
-                        if (2 * i + 1 < len) dst[tstride] = (unsigned short)(o >> 16);
-                    }
-                }
+                tc_store_out(r, reinterpret_cast<unsigned short*>(out_tile), ocol + (int64_t)t * kChunk * tstride, tstride, v, len);
             }
             // ---- state row v (thread = TMEM lane v of DST): S[v][k] = bf(fma(S[v][k], E_tot[k], DST[v][k])) in
             //      registers; the refreshed pairs go back to tensor memory for the next chunk's MMA1 ----
@@ -362,11 +282,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
                 seg_mine[i * 128] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
             __threadfence();
             named_barrier_sync(bar_id, 128);
-            if (v == 0) {
-                const int pos = atomicAdd(a.queue + 2, 1);
-                __threadfence();
-                *reinterpret_cast<volatile int32_t*>(a.qslots + pos) = item + (int)n_chains;
-            }
+            if (v == 0) tc_push_followup(a, item, n_chains);
             continue;
         }
         if (v == 0) atomicAdd(a.queue + 3, 1);  // this chain is finished

@@ -91,21 +91,10 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
     bool failed = false;
 
     for (int64_t chain = blockIdx.x; chain < n_chains && !failed; chain += gridDim.x) {
-        const int64_t n = chain / a.H;
-        const int h = (int)(chain - n * a.H);
-        int64_t bos, seq_len, tile_base;
-        if (a.cu_seqlens != nullptr) {
-            bos = a.cu_seqlens[n];
-            seq_len = a.cu_seqlens[n + 1] - bos;
-            if (seq_len < 0) seq_len = 0;
-            tile_base = a.tile_prefix[n];
-        } else {
-            bos = n * a.T;
-            seq_len = a.T;
-            tile_base = n * ((a.T + kChunk - 1) / kChunk);
-        }
-        const int n_chunks = (int)((seq_len + kChunk - 1) / kChunk);
-        const uint8_t* rec_base = a.workspace + ((int64_t)h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
+        const TcChain ch = tc_locate_chain(a, chain);
+        const int64_t n = ch.n, bos = ch.bos, seq_len = ch.seq_len;
+        const int h = ch.h, n_chunks = ch.n_chunks;
+        const uint8_t* rec_base = ch.rec_base;
         const int64_t st_base = (n * a.H + h) * (int64_t)(kD * kD) + v;  // S[vv][k = v] at st_base + vv * 128
 
         auto issue_load = [&](int t) {
@@ -169,40 +158,14 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                     __syncwarp();
                 }
                 unsigned short v_cur[kChunk];  // value column v of this chunk (zero past the sequence end)
-                {
-                    const unsigned short* vt = reinterpret_cast<const unsigned short*>(cs + kSmV + s * 4096) + v;
-#pragma unroll
-                    for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
-                }
-                uint32_t bpk[8];
-                {
-                    const float4* bp = reinterpret_cast<const float4*>(st + kTcBeta);
-#pragma unroll
-                    for (int i4 = 0; i4 < 4; ++i4) {
-                        const float4 b = bp[i4];
-                        bpk[2 * i4] = pack_bf2(b.x, b.y);
-                        bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
-                    }
-                }
+                tc_load_v_column(cs + kSmV + s * 4096, v, len, v_cur);
+                uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta)
+                tc_load_beta(st, bpk);
                 if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
                 mma_phase ^= 1u;
                 tc_fence_after_sync();
                 // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
-                {
-                    uint32_t r[16];
-                    tmem_ld16(t_d1 + lane_sel, r);
-                    tmem_wait_ld();
-                    uint32_t up[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                        const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
-                        up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
-                    }
-                    uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                    *reinterpret_cast<uint4*>(ap) = make_uint4(up[0], up[1], up[2], up[3]);
-                    *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(up[4], up[5], up[6], up[7]);
-                }
+                tc_form_u_prime(t_d1 + lane_sel, cs + kSmA23, v, v_cur, bpk);
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 named_barrier_sync(kBarMain, 128);
@@ -218,17 +181,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
                 mma_phase ^= 1u;
                 tc_fence_after_sync();
-                {
-                    uint32_t r[16];
-                    tmem_ld16(t_ds + lane_sel, r);
-                    tmem_wait_ld();
-                    uint8_t* ap = cs + kSmA23 + (v >> 3) * 128 + (v & 7) * 16;
-                    uint32_t p[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    *reinterpret_cast<uint4*>(ap) = make_uint4(p[0], p[1], p[2], p[3]);
-                    *reinterpret_cast<uint4*>(ap + 2048) = make_uint4(p[4], p[5], p[6], p[7]);
-                }
+                tc_form_u(t_ds + lane_sel, cs + kSmA23, v);  // U = bf(D2)
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 named_barrier_sync(kBarMain, 128);
@@ -254,19 +207,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 uint32_t r[32];
                 tmem_ld32(t_d1 + lane_sel, r);  // D3 in 0-15, o0 in 16-31
                 tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t o = bf2_add(pack_bf2(__uint_as_float(r[16 + 2 * i]), __uint_as_float(r[16 + 2 * i + 1])),
-                                               pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])));
-                    if (len == kChunk) {
-                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i) * kD + v] = (unsigned short)(o & 0xffffu);
-                        reinterpret_cast<unsigned short*>(out_tile)[(2 * i + 1) * kD + v] = (unsigned short)(o >> 16);
-                    } else {
-                        unsigned short* dst = ocol + ((int64_t)t * kChunk + 2 * i) * tstride;
-                        if (2 * i < len) dst[0] = (unsigned short)(o & 0xffffu);
-                        if (2 * i + 1 < len) dst[tstride] = (unsigned short)(o >> 16);
-                    }
-                }
+                tc_store_out(r, reinterpret_cast<unsigned short*>(out_tile), ocol + (int64_t)t * kChunk * tstride, tstride, v, len);
             }
             // ---- my rows of state column k ----
             if (wg == 0) wide_update<0, 2>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
