@@ -34,7 +34,7 @@ static_assert(kWsRecord == 13824, "workspace record size");
 //   B1  [kd; qd] as the K-major B operand [32 rows, K=128]: byte = (k/8)*528 + (r/8)*128 + (r%8)*16 + (k%8)*2
 //   KR  kr as the MN-major operand [128 k, 16 tokens]:      byte = (i/8)*2304 + (n/8)*144 + (i%8)*16 + (n%8)*2
 //   INV, MQK as K-major B operands [16, 16]:                byte = (j/8)*256 + (i/8)*128 + (i%8)*16 + (j%8)*2
-//   ET  E_tot [128] f32;  BETA bf16-rounded sigmoid(beta) [16] widened to f32
+//   ET  E_tot [128] f32;  BETA sigmoid(beta) [16] bf16 (in a 64-byte slot)
 constexpr int kTcB1Lbo = 528;                   // between the 16-byte K chunks of B1
 constexpr int kTcB1Bytes = 16 * kTcB1Lbo;       // 8448
 constexpr int kTcKrSbo = 144;                   // between 8-column groups of KR

@@ -120,7 +120,7 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
     if (lane < kChunk) {
         const float sb = sigmoid_tanh(pf.beta_logit);
         sm.beta_act[lane] = sb;
-        if constexpr (kTc) reinterpret_cast<float*>(ws + kTcBeta)[lane] = bf2f(f2bf(sb));
+        if constexpr (kTc) reinterpret_cast<__nv_bfloat16*>(ws + kTcBeta)[lane] = f2bf(sb);
     }
 
     float csum[4] = {0.f, 0.f, 0.f, 0.f};  // running in-chunk gate sum of my columns

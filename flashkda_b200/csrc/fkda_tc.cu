@@ -144,15 +144,12 @@ __device__ __forceinline__ void tc_push_followup(const TwoPassArgs& a, int item,
     *reinterpret_cast<volatile int32_t*>(a.qslots + pos) = item + (int)n_chains;
 }
 
-// sigmoid(beta) of the 16 rows as bf16x2 pairs (the record holds bf16-rounded fp32 values)
+// sigmoid(beta) of the 16 rows as bf16x2 pairs (the record holds them as 16 bf16 values)
 __device__ __forceinline__ void tc_load_beta(const uint8_t* rec, uint32_t (&bpk)[8]) {
-    const float4* bp = reinterpret_cast<const float4*>(rec + kTcBeta);
-#pragma unroll
-    for (int i4 = 0; i4 < 4; ++i4) {
-        const float4 b = bp[i4];
-        bpk[2 * i4] = pack_bf2(b.x, b.y);
-        bpk[2 * i4 + 1] = pack_bf2(b.z, b.w);
-    }
+    const uint4* bp = reinterpret_cast<const uint4*>(rec + kTcBeta);
+    const uint4 x = bp[0], y = bp[1];
+    bpk[0] = x.x; bpk[1] = x.y; bpk[2] = x.z; bpk[3] = x.w;
+    bpk[4] = y.x; bpk[5] = y.y; bpk[6] = y.z; bpk[7] = y.w;
 }
 // value column v of the chunk from the [16][128] tile (zero past the sequence end)
 __device__ __forceinline__ void tc_load_v_column(const uint8_t* v_tile, int v, int len, unsigned short (&v_cur)[kChunk]) {
