@@ -47,7 +47,8 @@ enum { FKDA_PHASE_PREPARE = 1, FKDA_PHASE_RECURRENCE = 2 };
 enum {
     FKDA_ALGO_AUTO = 0,
     FKDA_ALGO_TWOPASS = 1, /* prepare kernel -> HBM workspace -> recurrence kernel (CUDA cores) */
-    FKDA_ALGO_TC = 2       /* prepare kernel -> HBM workspace -> persistent tcgen05/TMEM recurrence */
+    FKDA_ALGO_TC = 2       /* prepare kernel -> HBM workspace -> persistent tcgen05/TMEM recurrence; a fixed batch
+                              with T == 1 (decode step) runs one state read-modify-write kernel instead */
 };
 
 /*
