@@ -59,3 +59,37 @@ def test_chunk_kda_dispatches_here_and_matches_triton(lens, monkeypatch):
     print(f"vs FLA Triton: out ratio {r_out:.3e}, state ratio {r_state:.3e}")
     assert r_out <= 0.008  # measured 5.9e-3 on N(0,1) inputs; the reference reports 3e-3..5e-3 on its own cases
     assert r_state <= 0.01
+
+
+def test_chunk_kda_decode_step_through_fla(monkeypatch):
+    """A decode step (one token per sequence, fixed batch) reaches the single-kernel decode path through the same
+    FLA call, and agrees with FLA's own kernels."""
+    fla_kda = pytest.importorskip("fla.ops.kda")
+    import flash_kda
+    import flashkda_b200
+    B, H = 16, 4
+    g = torch.Generator(device="cuda").manual_seed(11)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    q, k, v, gate = (r(B, 1, H, 128).to(torch.bfloat16) for _ in range(4))
+    beta = r(B, 1, H).to(torch.bfloat16)
+    A_log = torch.log(torch.empty(H, device="cuda").uniform_(1, 16, generator=g))
+    dt_bias = r(H * 128) * 0.1
+    h0 = r(B, H, 128, 128) * 0.05
+    kw = dict(q=q, k=k, v=v, g=gate, beta=beta, scale=1.0 / math.sqrt(128), initial_state=h0,
+              output_final_state=True, use_gate_in_kernel=True, use_qk_l2norm_in_kernel=True,
+              use_beta_sigmoid_in_kernel=True, safe_gate=True, A_log=A_log, dt_bias=dt_bias, lower_bound=-5.0,
+              transpose_state_layout=True)
+    with torch.inference_mode():
+        out_a, hT_a = fla_kda.chunk_kda(**kw)
+    torch.cuda.synchronize()
+    assert flashkda_b200.last_launch_count() == 1, "the decode step must run as one kernel"
+    try:
+        with torch.enable_grad():
+            out_b, hT_b = fla_kda.chunk_kda(**kw)
+        torch.cuda.synchronize()
+    except Exception as e:  # pragma: no cover - depends on the Triton build of the box
+        pytest.skip(f"FLA Triton path unavailable here: {type(e).__name__}: {e}")
+    r_out, r_state = oracle.err_ratio(out_b.float(), out_a.float()), oracle.err_ratio(hT_b.float(), hT_a.float())
+    print(f"decode vs FLA Triton: out ratio {r_out:.3e}, state ratio {r_state:.3e}")
+    assert r_out <= 0.01
+    assert r_state <= 0.01
