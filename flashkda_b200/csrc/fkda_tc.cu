@@ -156,8 +156,13 @@ __device__ __forceinline__ void tc_load_beta(const uint8_t* rec, uint32_t (&bpk)
 // value column v of the chunk from the [16][128] tile (zero past the sequence end)
 __device__ __forceinline__ void tc_load_v_column(const uint8_t* v_tile, int v, int len, unsigned short (&v_cur)[kChunk]) {
     const unsigned short* vt = reinterpret_cast<const unsigned short*>(v_tile) + v;
+    if (len == kChunk) {  // the common case without per-row masks
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
+        for (int i = 0; i < kChunk; ++i) v_cur[i] = vt[i * kD];
+    } else {
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v_cur[i] = (i < len) ? vt[i * kD] : (unsigned short)0;
+    }
 }
 // Row v of a [128, 16] K-major operand tile (the A operand of the 16-deep products): two 16-byte pieces.
 __device__ __forceinline__ void tc_store_a23_row(uint8_t* a23, int v, const uint32_t (&p)[8]) {
