@@ -74,6 +74,33 @@ __device__ __forceinline__ float row_sumsq(const float (&x)[4], int lane) {
     return __shfl_sync(0xffffffffu, c, lane | 1);                 // the odd lanes hold the group sums
 }
 
+// Sums of squares of TWO rows (q and k of one token) at once, each in the order of row_sumsq: after the pair
+// chains, the first butterfly step (groups 8 apart = lanes 16 apart) also splits the work, the lower half-warp
+// continuing with the q sums and the upper one with the k sums (a butterfly value is the same in both halves),
+// so the remaining three steps move one value per lane instead of two; 8 shuffles instead of 12.
+__device__ __forceinline__ void row_sumsq2(const float (&x)[4], const float (&y)[4], int lane, float* sx, float* sy) {
+    float px = 0.f, py = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        px = __fmaf_rn(x[i], x[i], px);
+        py = __fmaf_rn(y[i], y[i], py);
+    }
+    float cx = __shfl_sync(0xffffffffu, px, lane & ~1);  // partial of the even lane of my pair
+    float cy = __shfl_sync(0xffffffffu, py, lane & ~1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {                         // odd lanes: chain continued over their 4 columns
+        cx = __fmaf_rn(x[i], x[i], cx);
+        cy = __fmaf_rn(y[i], y[i], cy);
+    }
+    const bool upper = (lane & 16) != 0;
+    const float keep = upper ? cy : cx, send = upper ? cx : cy;
+    float c = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+#pragma unroll
+    for (int off = 8; off >= 2; off >>= 1) c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, off));
+    *sx = __shfl_sync(0xffffffffu, c, (lane & 15) | 1);        // odd lanes of the lower half hold the q total
+    *sy = __shfl_sync(0xffffffffu, c, (lane & 15) | 17);       // odd lanes of the upper half hold the k total
+}
+
 // What a warp fetches ahead of a chunk: the first kPf rows of q, k, g (my 4 columns), and the per-chunk
 // scalars.  Filled for the NEXT unit while the current one is in its last (memory-free) stage, so that a
 // chunk does not start with an exposed DRAM round trip.
@@ -146,8 +173,10 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         const float kv[4] = {bf_lo(kraw.x), bf_hi(kraw.x), bf_lo(kraw.y), bf_hi(kraw.y)};
         const float gv[4] = {bf_lo(graw.x), bf_hi(graw.x), bf_lo(graw.y), bf_hi(graw.y)};
         // q/k L2 normalisation
-        const float qinv = rsqrt_approx(__fadd_rn(row_sumsq(qv, lane), 1e-6f));
-        const float kinv = rsqrt_approx(__fadd_rn(row_sumsq(kv, lane), 1e-6f));
+        float qss, kss;
+        row_sumsq2(qv, kv, lane, &qss, &kss);
+        const float qinv = rsqrt_approx(__fadd_rn(qss, 1e-6f));
+        const float kinv = rsqrt_approx(__fadd_rn(kss, 1e-6f));
         const uint32_t qn0 = pack_bf2(__fmul_rn(qv[0], qinv), __fmul_rn(qv[1], qinv));
         const uint32_t qn1 = pack_bf2(__fmul_rn(qv[2], qinv), __fmul_rn(qv[3], qinv));
         const uint32_t kn0 = pack_bf2(__fmul_rn(kv[0], kinv), __fmul_rn(kv[1], kinv));
