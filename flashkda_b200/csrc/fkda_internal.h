@@ -26,6 +26,9 @@ struct TwoPassArgs {
     int32_t* qslots;       // segment queue: slot i receives the i-th pushed item (-1 = not yet pushed)
     uint32_t* seg_state;   // [chain][16][128] uint4: bf16 state handed from one segment of a chain to the next
     int32_t seg_chunks;    // chunks per scheduling segment (0 = whole chains)
+    int32_t slab_c0, slab_chunks;  // fixed batches only: this launch covers chunks [slab_c0, slab_c0 + slab_chunks) of
+                                   // every sequence (slab_chunks == 0: all chunks); a chain's state travels from one
+                                   // slab to the next through seg_state
     int64_t T, H, N, total_tiles;
     int64_t token_stride, beta_token_stride;
     float scale, gate_scale;

@@ -314,44 +314,53 @@ __global__ void __launch_bounds__(kPwWarpsPerCta * 32, 1) prepare_warp_kernel(co
     extern __shared__ __align__(16) uint8_t pw_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     PrepWarpSmem& sm = reinterpret_cast<PrepWarpSmem*>(pw_smem)[warp];
-    const int64_t n_units = a.total_tiles * a.H;
+    // units = (chunk, head) pairs, head fastest; with a slab (fixed batches) only chunks [slab_c0, slab_c0 +
+    // slab_chunks) of every sequence, enumerated densely
+    const int64_t tps = (a.T + kChunk - 1) / kChunk;  // chunks per sequence of a fixed batch
+    const int64_t n_units = (a.slab_chunks > 0 ? a.N * (int64_t)a.slab_chunks : a.total_tiles) * a.H;
     const int64_t stride = (int64_t)gridDim.x * kPwWarpsPerCta;
     // units past the last chunk of a ragged batch (upper-bound tile count) all sit at the end of the range
-    auto locate = [&](int64_t u, int64_t* t0, int* len, int* h) {
+    auto locate = [&](int64_t u, int64_t* tile, int64_t* t0, int* len, int* h) {
         if (u >= n_units) return false;
-        const int64_t tile = u / a.H;
-        *h = (int)(u - tile * a.H);
-        return locate_tile(a, tile, t0, len);
+        int64_t t = u / a.H;
+        *h = (int)(u - t * a.H);
+        if (a.slab_chunks > 0) {
+            const int64_t n = t / a.slab_chunks;
+            t = n * tps + a.slab_c0 + (t - n * a.slab_chunks);
+        }
+        *tile = t;
+        return locate_tile(a, t, t0, len);
     };
     int64_t u = (int64_t)blockIdx.x * kPwWarpsPerCta + warp;
-    int64_t t0 = 0, t0n = 0;
+    int64_t tile = 0, tile_n = 0, t0 = 0, t0n = 0;
     int len = 0, h = 0, lenn = 0, hn = 0;
-    bool valid = locate(u, &t0, &len, &h);
+    bool valid = locate(u, &tile, &t0, &len, &h);
     PrepPrefetch pf;
     if (valid) prep_prefetch(a, t0, len, h, lane, pf);
     while (valid) {
-        const bool next_valid = locate(u + stride, &t0n, &lenn, &hn);
-        const int64_t tile = u / a.H;
+        const bool next_valid = locate(u + stride, &tile_n, &t0n, &lenn, &hn);
         uint8_t* ws = a.workspace + ((int64_t)h * a.total_tiles + tile) * (int64_t)(kTc ? kTcRecord : kWsRecord);
         prepare_chunk_warp<kTc>(a, t0, len, h, ws, sm, lane, pf, next_valid, t0n, lenn, hn);
         u += stride;
         valid = next_valid;
-        t0 = t0n; len = lenn; h = hn;
+        tile = tile_n; t0 = t0n; len = lenn; h = hn;
     }
     sm100::bulk_wait_group<0>();  // (lane 0) the last records have landed
 }
 
+// max_ctas > 0 caps the grid (a launch that shares the GPU with a concurrent recurrence kernel)
 template <bool kTc>
-inline int launch_prepare_warp(const TwoPassArgs& a, cudaStream_t stream) {
+inline int launch_prepare_warp(const TwoPassArgs& a, cudaStream_t stream, int max_ctas = 0) {
     const int smem = (int)sizeof(PrepWarpSmem) * kPwWarpsPerCta;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaFuncSetAttribute(prepare_warp_kernel<kTc>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return FKDA_ERR_LAUNCH;
-    const int64_t n_units = a.total_tiles * a.H;
+    const int64_t n_units = (a.slab_chunks > 0 ? a.N * (int64_t)a.slab_chunks : a.total_tiles) * a.H;
     int64_t ctas = (n_units + kPwWarpsPerCta - 1) / kPwWarpsPerCta;
     if (ctas > sms) ctas = sms;
+    if (max_ctas > 0 && ctas > max_ctas) ctas = max_ctas;
     if (ctas < 1) ctas = 1;
     prepare_warp_kernel<kTc><<<(unsigned)ctas, kPwWarpsPerCta * 32, smem, stream>>>(a);
     return FKDA_OK;

@@ -24,6 +24,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
 #include "fkda_prepare_warp.cuh"
@@ -540,28 +542,63 @@ namespace fkda {
 // Segment scheduling is used when there are more chains than a B200 can hold at once (3 per SM);
 // with fewer chains every chain has its own slot and whole chains are the work items.
 constexpr int64_t kSegThresholdChains = 384;
-constexpr int kSegChunks = 64;  // even, so that the double-buffer parity of a segment's first chunk is fixed
-// tuning aid: $FKDA_SEG_CHUNKS overrides the segment length (read once per process)
-static int seg_chunks_setting() {
-    static int v = 0;
-    if (v == 0) {
-        v = kSegChunks;
+constexpr int kSegChunksMax = 64, kSegChunksMin = 16;
+// Segment length: 64 chunks when there is plenty of work (the hand-over of a 32 KB state costs about one chunk
+// step), shorter when the whole problem is only a few segments per chain slot, so that 512 chains of 64 chunks
+// do not run as one full round plus a nearly empty one.  Even, so that the double-buffer parity of a segment's
+// first chunk is fixed.  A function of (T_total, H, N) only: the workspace is sized with the same value.
+// Tuning aid: $FKDA_SEG_CHUNKS overrides it (read once per process).
+static int seg_chunks_for(int64_t T_total, int64_t H, int64_t N) {
+    static int forced = -1;
+    if (forced < 0) {
+        forced = 0;
         if (const char* e = getenv("FKDA_SEG_CHUNKS")) {
             const int x = atoi(e) / 2 * 2;
-            if (x >= 2) v = x;
+            if (x >= 2) forced = x;
         }
     }
-    return v;
+    if (forced > 0) return forced;
+    const int64_t chain_slots = 148 * kTcChains;
+    int64_t seg = H * ws_tiles_upper_bound(T_total, N) / (4 * chain_slots);  // aim at >= 4 segments per chain slot
+    seg = seg / 2 * 2;
+    if (seg > kSegChunksMax) seg = kSegChunksMax;
+    if (seg < kSegChunksMin) seg = kSegChunksMin;
+    return (int)seg;
 }
 static bool use_segments(int64_t H, int64_t N) { return H * N > kSegThresholdChains; }
 static size_t seg_slot_count(int64_t T_total, int64_t H, int64_t N) {
     // one push per segment after the first of each chain, plus one ticket per resident warpgroup at the end
-    return (size_t)(H * (ws_tiles_upper_bound(T_total, N) / seg_chunks_setting() + N) + 4096);
+    return (size_t)(H * (ws_tiles_upper_bound(T_total, N) / seg_chunks_for(T_total, H, N) + N) + 4096);
 }
 static size_t seg_slots_bytes(int64_t T_total, int64_t H, int64_t N) {
     return use_segments(H, N) ? (seg_slot_count(T_total, H, N) * 4 + 255) / 256 * 256 : 0;
 }
-static size_t seg_state_bytes(int64_t H, int64_t N) { return use_segments(H, N) ? (size_t)(H * N) * 32768 : 0; }
+// hand-over states (32 KB per chain): between the segments of the work queue, or between the slabs of a
+// pipelined forward
+static size_t seg_state_bytes(int64_t H, int64_t N) { return (size_t)(H * N) * 32768; }
+
+// Side stream and events of the slab pipeline, one set per device, created on first use.
+constexpr int kMaxSlabs = 4;
+struct SlabStreams {
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork = nullptr, done[kMaxSlabs] = {nullptr, nullptr, nullptr, nullptr};
+    bool ready = false;
+};
+static SlabStreams* slab_streams(int dev) {
+    static std::mutex mu;
+    static SlabStreams table[64];
+    if (dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    SlabStreams& t = table[dev];
+    if (!t.ready) {
+        if (cudaStreamCreateWithFlags(&t.side, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        for (int i = 0; i < kMaxSlabs; ++i)
+            if (cudaEventCreateWithFlags(&t.done[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        t.ready = true;
+    }
+    return &t;
+}
 
 size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
     return kWsHeaderBytes + ws_prefix_bytes(N) + seg_slots_bytes(T_total, H, N) + seg_state_bytes(H, N) +
@@ -612,11 +649,63 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         if (use_segments(p.H, p.N)) {
             a.qslots = reinterpret_cast<int32_t*>(base);
             a.seg_state = reinterpret_cast<uint32_t*>(base + slots);
-            a.seg_chunks = seg_chunks_setting();
+            a.seg_chunks = seg_chunks_for(T_total, p.H, p.N);
             if (do_rec && cudaMemsetAsync(a.qslots, 0xff, slots, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;
         }
+        a.seg_state = reinterpret_cast<uint32_t*>(base + slots);
         a.workspace = base + slots + states;
     }
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return FKDA_ERR_LAUNCH;
+    const int64_t chains = p.N * p.H;
+    const bool wide = chains <= sms && getenv("FKDA_TC_NO_WIDE") == nullptr;  // (the switch is a tuning aid)
+    TcMaps maps;
+    if (do_rec && (!encode_token_map(&maps.v, p.v, p.B * p.T, p.H, p.token_stride) ||
+                   !encode_token_map(&maps.out, p.out, p.B * p.T, p.H, p.token_stride)))
+        return FKDA_ERR_LAUNCH;
+    const int wide_smem = kSmChainBytes + (int)sizeof(TcWideCtrl) + 128;
+    if (do_rec && wide &&
+        cudaFuncSetAttribute(recurrence_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem) != cudaSuccess)
+        return FKDA_ERR_LAUNCH;
+
+    // ---- few chains on a fixed batch: the recurrence is a serial walk on `chains` SMs and leaves the others
+    //      idle, so the forward is cut into slabs of chunks and the prepare stage of slab i+1 runs on the idle SMs
+    //      (side stream) while the recurrence walks slab i; the state of a chain travels through seg_state.
+    //      Only stream order and events connect the launches: no kernel waits for another one. ----
+    const int64_t tps = (p.T + kChunk - 1) / kChunk;
+    const int idle_sms = sms - (int)chains;
+    if (wide && !varlen && p.phase_mask == 0 && idle_sms >= 32 && tps >= 64 && getenv("FKDA_TC_NO_SLABS") == nullptr) {
+        SlabStreams* ss = slab_streams(dev);
+        if (ss == nullptr) return FKDA_ERR_LAUNCH;
+        const int n_slabs = tps >= 256 ? kMaxSlabs : 2;
+        const int slab_len = (int)(((tps + n_slabs - 1) / n_slabs + 1) / 2 * 2);  // even
+        auto slab_args = [&](int i) {
+            TwoPassArgs x = a;
+            x.slab_c0 = i * slab_len;
+            x.slab_chunks = (int)((int64_t)x.slab_c0 + slab_len <= tps ? slab_len : tps - x.slab_c0);
+            return x;
+        };
+        if (launch_prepare_warp<true>(slab_args(0), stream) != FKDA_OK) return FKDA_ERR_LAUNCH;
+        ++launches;
+        if (cudaEventRecord(ss->fork, stream) != cudaSuccess || cudaStreamWaitEvent(ss->side, ss->fork, 0) != cudaSuccess)
+            return FKDA_ERR_LAUNCH;
+        for (int i = 1; i < n_slabs && (int64_t)i * slab_len < tps; ++i) {
+            if (launch_prepare_warp<true>(slab_args(i), ss->side, idle_sms) != FKDA_OK) return FKDA_ERR_LAUNCH;
+            ++launches;
+            if (cudaEventRecord(ss->done[i], ss->side) != cudaSuccess) return FKDA_ERR_LAUNCH;
+        }
+        for (int i = 0; i < n_slabs && (int64_t)i * slab_len < tps; ++i) {
+            if (i > 0 && cudaStreamWaitEvent(stream, ss->done[i], 0) != cudaSuccess) return FKDA_ERR_LAUNCH;
+            recurrence_tc_wide_kernel<<<(unsigned)chains, 384, wide_smem, stream>>>(slab_args(i), maps);
+            ++launches;
+        }
+        if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
+        *n_launches = launches;
+        return FKDA_OK;
+    }
+
     if (varlen && do_prep) {
         launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, stream);
         ++launches;
@@ -626,30 +715,16 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         ++launches;
     }
     if (do_rec) {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            return FKDA_ERR_LAUNCH;
-        if (cudaFuncSetAttribute(recurrence_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
-            cudaSuccess)
-            return FKDA_ERR_LAUNCH;
-        const int64_t chains = p.N * p.H;
         int64_t ctas = chains;  // one chain per SM while they last, then two, then three
         if (ctas > sms) ctas = sms;
         if (ctas < 1) ctas = 1;
-        TcMaps maps;
-        if (!encode_token_map(&maps.v, p.v, p.B * p.T, p.H, p.token_stride) ||
-            !encode_token_map(&maps.out, p.out, p.B * p.T, p.H, p.token_stride))
-            return FKDA_ERR_LAUNCH;
-        const bool no_wide = getenv("FKDA_TC_NO_WIDE") != nullptr;  // tuning aid
-        if (chains <= sms && !no_wide) {
+        if (wide) {
             // few chains: one per CTA, the idle warpgroups help with the state update
-            const int wide_smem = kSmChainBytes + (int)sizeof(TcWideCtrl) + 128;
-            if (cudaFuncSetAttribute(recurrence_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem) !=
-                cudaSuccess)
-                return FKDA_ERR_LAUNCH;
             recurrence_tc_wide_kernel<<<(unsigned)ctas, 384, wide_smem, stream>>>(a, maps);
         } else if (getenv("FKDA_TC_TS") == nullptr) {
+            if (cudaFuncSetAttribute(recurrence_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
+                cudaSuccess)
+                return FKDA_ERR_LAUNCH;
             recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a, maps);
         } else {
             // opt-in variant with the state's MMA copy in tensor memory (same speed, 98 KB less shared memory)

@@ -96,6 +96,10 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         const int h = ch.h, n_chunks = ch.n_chunks;
         const uint8_t* rec_base = ch.rec_base;
         const int64_t st_base = (n * a.H + h) * (int64_t)(kD * kD) + v;  // S[vv][k = v] at st_base + vv * 128
+        // chunk range of this launch: all chunks, or one slab of a pipelined forward (fixed batches)
+        const int c0 = a.slab_chunks > 0 ? a.slab_c0 : 0;
+        const int c1 = (a.slab_chunks > 0 && c0 + a.slab_chunks < n_chunks) ? c0 + a.slab_chunks : n_chunks;
+        uint4* const seg_mine = reinterpret_cast<uint4*>(a.seg_state) + (chain * 16) * 128 + v;  // + i * 128
 
         auto issue_load = [&](int t) {
             const int s = t % kTcStages;
@@ -104,7 +108,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
             tma_load_3d(cs + kSmV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[s]);
         };
         if (threadIdx.x == 0) {
-            for (int t = 0; t < kTcStages && t < n_chunks; ++t) issue_load(t);
+            for (int t = c0; t < c0 + kTcStages && t < c1; ++t) issue_load(t);
         }
         const int64_t tstride = a.token_stride;
         unsigned short* ocol = reinterpret_cast<unsigned short*>(a.out) + bos * tstride + (int64_t)h * kD + v;
@@ -112,15 +116,26 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         // ---- initial state: my rows of column k into registers (pairs over v) and into the S^T tile ----
         uint32_t sreg[64];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-            sreg[i] = 0u;
-            if ((i >> 3) >= b_lo && (i >> 3) < b_hi && a.initial_state != nullptr) {
-                if (a.state_fp32) {
-                    const float* src = reinterpret_cast<const float*>(a.initial_state) + st_base;
-                    sreg[i] = pack_bf2(src[(2 * i) * kD], src[(2 * i + 1) * kD]);
-                } else {
-                    const unsigned short* src = reinterpret_cast<const unsigned short*>(a.initial_state) + st_base;
-                    sreg[i] = (uint32_t)src[(2 * i) * kD] | ((uint32_t)src[(2 * i + 1) * kD] << 16);
+        for (int i = 0; i < 64; ++i) sreg[i] = 0u;
+        if (c0 > 0) {  // handed over by the launch that ran the previous slab
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if ((i >> 1) >= b_lo && (i >> 1) < b_hi) {
+                    const uint4 x = __ldcg(seg_mine + i * 128);
+                    sreg[4 * i] = x.x; sreg[4 * i + 1] = x.y; sreg[4 * i + 2] = x.z; sreg[4 * i + 3] = x.w;
+                }
+            }
+        } else if (a.initial_state != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                if ((i >> 3) >= b_lo && (i >> 3) < b_hi) {
+                    if (a.state_fp32) {
+                        const float* src = reinterpret_cast<const float*>(a.initial_state) + st_base;
+                        sreg[i] = pack_bf2(src[(2 * i) * kD], src[(2 * i + 1) * kD]);
+                    } else {
+                        const unsigned short* src = reinterpret_cast<const unsigned short*>(a.initial_state) + st_base;
+                        sreg[i] = (uint32_t)src[(2 * i) * kD] | ((uint32_t)src[(2 * i + 1) * kD] << 16);
+                    }
                 }
             }
         }
@@ -133,7 +148,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         named_barrier_sync(kBarAll, 384);
         __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kSmOut);
 
-        for (int t = 0; t < n_chunks; ++t) {
+        for (int t = c0; t < c1; ++t) {
             const int s = t % kTcStages;
             uint8_t* st = cs + kSmStage + s * kSmStageBytes;
             const uint32_t st_addr = smem_u32(st);
@@ -223,14 +238,19 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                         tma_store_3d(&maps.out, 0, h, (int)(bos + (int64_t)t * kChunk), out_tile);
                         bulk_commit_group();
                     }
-                    if (t + kTcStages < n_chunks) issue_load(t + kTcStages);
+                    if (t + kTcStages < c1) issue_load(t + kTcStages);
                 }
                 __syncwarp();
             }
         }
         if (failed) break;
-        // ---- final state: my rows of my column, bf16 or widened to fp32 ----
-        if (a.final_state != nullptr) {
+        if (c1 < n_chunks) {  // not the last slab: my rows of the state to the hand-over buffer
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if ((i >> 1) >= b_lo && (i >> 1) < b_hi)
+                    seg_mine[i * 128] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
+        } else if (a.final_state != nullptr) {
+            // ---- final state: my rows of my column, bf16 or widened to fp32 ----
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
                 if ((i >> 3) >= b_lo && (i >> 3) < b_hi) {

@@ -240,6 +240,8 @@ void fill_args(const fkda_fwd_params& p, TwoPassArgs* out) {
     a.qslots = nullptr;
     a.seg_state = nullptr;
     a.seg_chunks = 0;
+    a.slab_c0 = 0;
+    a.slab_chunks = 0;
     a.tile_prefix = reinterpret_cast<int32_t*>(base + kWsHeaderBytes);
     a.workspace = base + kWsHeaderBytes + ws_prefix_bytes(p.N);
 }

@@ -63,6 +63,15 @@ def varlen_lengths(n: int = 64, max_len: int = 4096, seed: int = 0) -> List[int]
     return lens
 
 
+def _parse_lens(txt: str) -> List[int]:
+    """``"1300+547+2048"`` or ``"1024x8"`` (eight sequences of 1024 tokens)."""
+    txt = txt.replace("x", "*")
+    if "*" in txt:
+        length, count = txt.split("*")
+        return [int(length)] * int(count)
+    return [int(x) for x in txt.split("+")]
+
+
 def config(name: str) -> Workload:
     """The five benchmark configurations, by short name."""
     if name == "cfg1":   # CPU-runnable case
@@ -77,9 +86,13 @@ def config(name: str) -> Workload:
         return Workload("cfg4", B=8, T=32768, H=64, lower_bound=-3.0, state_in="fp32", state_out="fp32")
     if name == "cfg5":   # one long sequence (context-parallel case)
         return Workload("cfg5", B=1, T=1048576, H=32, lower_bound=-5.0, state_out="fp32")
-    if "=" in name:      # ad-hoc shape, e.g. "B=1,T=4096,H=444,state=fp32,lb=-5"
+    if "=" in name:      # ad-hoc shape, e.g. "B=1,T=4096,H=444,state=fp32,lb=-5" or "H=64,lens=1300+547+2048,state=fp32"
         kv = dict(item.split("=") for item in name.split(","))
         st = kv.get("state")
+        if "lens" in kv:  # ragged batch: B = 1, T = total tokens
+            lens = _parse_lens(kv["lens"])
+            return Workload(name, B=1, T=sum(lens), H=int(kv["H"]), lower_bound=float(kv.get("lb", -5.0)),
+                            state_in=st, state_out=st, seq_lens=lens)
         return Workload(name, B=int(kv.get("B", 1)), T=int(kv["T"]), H=int(kv["H"]),
                         lower_bound=float(kv.get("lb", -5.0)), state_in=st, state_out=st)
     raise KeyError(name)

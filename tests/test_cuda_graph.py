@@ -10,8 +10,11 @@ from flashkda_b200.synth import Workload, make_inputs, to_device
 pytestmark = pytest.mark.gpu
 
 
-def test_capture_and_replay():
-    w = Workload("graph", 4, 96, 4, state_in="fp32", state_out="fp32")
+@pytest.mark.parametrize("B,T", [(4, 96), (1, 2048)], ids=["short", "slab_pipeline"])
+def test_capture_and_replay(B, T):
+    """The second shape takes the slab pipeline (few chains, long sequence): its side stream forks from and
+    joins back into the captured stream through events."""
+    w = Workload("graph", B, T, 4, state_in="fp32", state_out="fp32")
     d = to_device(make_inputs(w, seed=3), "cuda")
     ws = torch.empty(flashkda_b200.get_workspace_size(w.tokens, w.H, w.n_seqs), dtype=torch.uint8, device="cuda")
 

@@ -298,3 +298,21 @@ def test_recurrence_kernel_variants_agree(monkeypatch):
     out_s2, hT_s2 = run_gpu(inp2, "tc")
     assert oracle.err_ratio(out_t2, out_s2) <= 2e-3
     assert oracle.err_ratio(hT_t2, hT_s2) <= 1e-3
+
+
+@pytest.mark.parametrize("B,T,H", [(1, 8192, 8), (2, 2100, 4), (1, 1030, 32)])
+def test_slab_pipeline_matches_single_pass(B, T, H, monkeypatch):
+    """Few chains on a fixed batch: the forward runs as slabs of chunks, the prepare stage of the next slab on the
+    idle SMs (side stream) while the recurrence walks the current one, chain states handed from slab to slab.
+    Same kernels, same numbers as the two-launch form."""
+    w = Workload("slab", B, T, H, state_in="fp32", state_out="fp32", lower_bound=-1.0)
+    inp = make_inputs(w, seed=31)
+    out_p, hT_p = run_gpu(inp, "tc")
+    n_pipe = flashkda_b200.last_launch_count()
+    monkeypatch.setenv("FKDA_TC_NO_SLABS", "1")
+    out_s, hT_s = run_gpu(inp, "tc")
+    assert flashkda_b200.last_launch_count() == 2 and n_pipe in (4, 8)
+    assert torch.equal(out_p, out_s) and torch.equal(hT_p, hT_s)
+    if T <= 2100:
+        ref_out, ref_hT = run_oracle(inp)
+        check_against(out_p, hT_p, ref_out, ref_hT)
