@@ -76,6 +76,15 @@ __device__ __forceinline__ float sigmoid_tanh(float x) {
     return __fmaf_rn(th, 0.5f, 0.5f);
 }
 
+// Two independent fp32 fused multiply-adds in one instruction (sm_100 packed fp32 pipe): d = a * b + c per half,
+// each rounded to nearest-even exactly like fma.rn.f32.
+__device__ __forceinline__ void fma2_rn(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2,%3};\nmov.b64 rb, {%4,%5};\nmov.b64 rc, {%6,%7};\n"
+        "fma.rn.ftz.f32x2 rd, ra, rb, rc;\nmov.b64 {%0,%1}, rd;\n}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+
 // ---- bf16 helpers: every op rounds to nearest-even once ----
 __device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ __nv_bfloat16 f2bf(float x) { return __float2bfloat16_rn(x); }

@@ -721,13 +721,14 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         if (wide) {
             // few chains: one per CTA, the idle warpgroups help with the state update
             recurrence_tc_wide_kernel<<<(unsigned)ctas, 384, wide_smem, stream>>>(a, maps);
-        } else if (getenv("FKDA_TC_TS") == nullptr) {
+        } else if (getenv("FKDA_TC_SS") != nullptr) {
+            // the variant that keeps the state's MMA copy and the 16-deep operands in shared memory
             if (cudaFuncSetAttribute(recurrence_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
                 cudaSuccess)
                 return FKDA_ERR_LAUNCH;
             recurrence_tc_kernel<<<(unsigned)ctas, kTcChains * 128, kTcSmemBytes, stream>>>(a, maps);
         } else {
-            // opt-in variant with the state's MMA copy in tensor memory (same speed, 98 KB less shared memory)
+            // default: state copy and 16-deep A operands in tensor memory
             if (cudaFuncSetAttribute(recurrence_tc_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmemBytes) !=
                 cudaSuccess)
                 return FKDA_ERR_LAUNCH;

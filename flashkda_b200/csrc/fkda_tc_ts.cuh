@@ -19,9 +19,8 @@ namespace fkda {
 // byte offsets inside one chain's shared-memory block (no state tile)
 constexpr int kTsStage = 0;                                   // kTcStages chunk records
 constexpr int kTsV = kTsStage + kTcStages * kSmStageBytes;    // kTcStages value tiles [16][128] bf16
-constexpr int kTsA23 = kTsV + kTcStages * 4096;               // A operand of the 16-deep products [128, 16];
-constexpr int kTsOut = kTsA23;                                // also the out tile [16][128] bf16
-constexpr int kTsChainBytes = kTsA23 + 4096;
+constexpr int kTsOut = kTsV + kTcStages * 4096;               // out tile [16][128] bf16
+constexpr int kTsChainBytes = kTsOut + 4096;
 static_assert(kTsV % 128 == 0 && kTsChainBytes % 128 == 0, "TMA tiles are 128-byte aligned");
 constexpr int kTsSmemBytes = kTcChains * kTsChainBytes + (int)sizeof(TcCtrl) + 128;
 
@@ -60,13 +59,14 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_ds = tmem_base + 128u * wg;
     const uint32_t t_d1 = tmem_base + 384u + 32u * wg;
+    // the A operands of the 16-deep products (u', then U: [V = 128 lanes, 16 tokens] bf16 = 8 columns) also live
+    // in tensor memory, written by their owner threads: no shared-memory operand tile, no proxy fences
+    const uint32_t t_a = tmem_base + 480u + 8u * wg;
 
     constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, false, false);   // A = state copy in TMEM
     constexpr uint32_t idesc_n16 = make_idesc_bf16_f32(128, 16, false, false);
     constexpr uint32_t idesc_dst = make_idesc_bf16_f32(128, 128, false, true);   // B = kr tile, N-major
 
-    const uint32_t a23_addr = smem_u32(cs + kTsA23);
-    const uint64_t a23_desc = make_smem_desc(a23_addr, 2048, 128);
     const int bar_id = 1 + wg;
     const int64_t n_chains = a.N * a.H;
     uint32_t full_phase[kTcStages] = {0, 0};
@@ -159,9 +159,6 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T, A = the state copy in tensor memory (8 columns per K step) ----
             if (wiw == 0) {
                 if (elect_one()) {
-                    // the previous out tile shares the A23 tile: its TMA store must have read it before anybody
-                    // (released by this MMA's completion) writes u' there
-                    bulk_wait_group_read<0>();
                     tc_fence_after_sync();
                     const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, kTcB1Lbo, 128);
 #pragma unroll
@@ -182,8 +179,20 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             tc_fence_after_sync();
 
             // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
-            tc_form_u_prime(t_d1 + lane_sel, cs + kTsA23, v, v_cur, bpk);
-            fence_proxy_async_smem();
+            {
+                uint32_t r[16];
+                tmem_ld16(t_d1 + lane_sel, r);
+                tmem_wait_ld();
+                uint32_t up[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
+                    up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
+                }
+                tmem_st8(t_a + lane_sel, up[0], up[1], up[2], up[3], up[4], up[5], up[6], up[7]);
+                tmem_wait_st();
+            }
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
 
@@ -191,7 +200,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             if (wiw == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
-                    umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
+                    umma_ts(t_ds, t_a, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
                     umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();
@@ -199,8 +208,16 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
-            tc_form_u(t_ds + lane_sel, cs + kTsA23, v);  // U = bf(D2)
-            fence_proxy_async_smem();
+            {   // U = bf(D2) replaces u' as the A operand
+                uint32_t r[16];
+                tmem_ld16(t_ds + lane_sel, r);
+                tmem_wait_ld();
+                uint32_t p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                tmem_st8(t_a + lane_sel, p[0], p[1], p[2], p[3], p[4], p[5], p[6], p[7]);
+                tmem_wait_st();
+            }
             tc_fence_before_sync();
             named_barrier_sync(bar_id, 128);
 
@@ -208,8 +225,11 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             if (wiw == 0) {
                 if (elect_one()) {
                     tc_fence_after_sync();
-                    umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
-                    umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcKr, kTcKrLbo, kTcKrSbo), idesc_dst, 0u);
+                    // the previous out tile must have been read by its TMA store before this chunk's is formed
+                    // (by all threads, once this commit has released them)
+                    bulk_wait_group_read<0>();
+                    umma_ts(t_d1, t_a, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
+                    umma_ts(t_ds, t_a, make_smem_desc(st_addr + kTcKr, kTcKrLbo, kTcKrSbo), idesc_dst, 0u);
                     umma_commit(&ctl.mma[wg]);
                 }
                 __syncwarp();

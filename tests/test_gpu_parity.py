@@ -270,9 +270,10 @@ def test_segment_scheduling_fixed_batch():
 
 
 def test_recurrence_kernel_variants_agree(monkeypatch):
-    """The tensor-core recurrence has three kernels: three chains per CTA (default when there are more chains
-    than SMs), one chain per CTA with the idle warpgroups sharing the state update (few chains), and an
-    opt-in variant that keeps the state's MMA copy in tensor memory.  All three follow the same numerics."""
+    """The tensor-core recurrence has three kernels: three chains per CTA with the state's MMA copy in tensor
+    memory (default when there are more chains than SMs), the same with that copy in shared memory
+    (FKDA_TC_SS), and one chain per CTA with the idle warpgroups sharing the state update (few chains).
+    All three follow the same numerics."""
     lens = [700, 16, 1, 333, 2048]
     w = Workload("var", 1, sum(lens), 6, state_in="fp32", state_out="fp32", seq_lens=lens)
     inp = make_inputs(w, seed=21)
@@ -280,22 +281,22 @@ def test_recurrence_kernel_variants_agree(monkeypatch):
     out_w, hT_w = run_gpu(inp, "tc")                       # 30 chains: the one-chain-per-CTA kernel
     check_against(out_w, hT_w, ref_out, ref_hT)
     monkeypatch.setenv("FKDA_TC_NO_WIDE", "1")
-    out_s, hT_s = run_gpu(inp, "tc")                       # three chains per CTA
-    assert torch.equal(out_s, out_w) and torch.equal(hT_s, hT_w)
-    monkeypatch.setenv("FKDA_TC_TS", "1")
-    out_t, hT_t = run_gpu(inp, "tc")                       # state copy in tensor memory
+    out_t, hT_t = run_gpu(inp, "tc")                       # three chains per CTA, state copy in tensor memory
     check_against(out_t, hT_t, ref_out, ref_hT)
+    monkeypatch.setenv("FKDA_TC_SS", "1")
+    out_s, hT_s = run_gpu(inp, "tc")                       # three chains per CTA, state copy in shared memory
+    assert torch.equal(out_s, out_w) and torch.equal(hT_s, hT_w)
     mism = (out_t != out_s).float().mean().item()
-    print(f"tensor-memory state variant vs default: out mismatch {mism:.3e}")
+    print(f"tensor-memory state variant vs shared-memory variant: out mismatch {mism:.3e}")
     assert oracle.err_ratio(out_t, out_s) <= 2e-3
     assert oracle.err_ratio(hT_t, hT_s) <= 1e-3
-    # bf16 states and the segment queue (more than 384 chains) through the tensor-memory variant
+    # bf16 states and the segment queue (more than 384 chains) through both variants
     lens2 = torch.randint(1, 1500, (70,), generator=torch.Generator().manual_seed(3)).tolist()
     w2 = Workload("var2", 1, sum(lens2), 6, state_in="bf16", state_out="bf16", seq_lens=lens2)
     inp2 = make_inputs(w2, seed=22)
-    out_t2, hT_t2 = run_gpu(inp2, "tc")
-    monkeypatch.delenv("FKDA_TC_TS")
     out_s2, hT_s2 = run_gpu(inp2, "tc")
+    monkeypatch.delenv("FKDA_TC_SS")
+    out_t2, hT_t2 = run_gpu(inp2, "tc")
     assert oracle.err_ratio(out_t2, out_s2) <= 2e-3
     assert oracle.err_ratio(hT_t2, hT_s2) <= 1e-3
 
