@@ -298,13 +298,15 @@ def run_ours(a):
 
     # ---- each kernel of the forward alone (CUDA events on the launching stream); the slower one is
     #      the dominant kernel the roofline line describes ----
-    # (the tensor-core recurrence has a one-chain-per-CTA variant that the launcher picks when there
-    #  are no more (sequence, head) chains than SMs)
+    # (the tensor-core recurrence has a one-chain-per-CTA variant that the launcher picks when there are no more
+    #  (sequence, head) chains than SMs; otherwise the three-chains-per-CTA kernel with the state copy in tensor
+    #  memory runs, or its shared-memory sibling when $FKDA_TC_SS is set)
     n_seqs = (len(inp["cu_seqlens"]) - 1) if inp.get("cu_seqlens") is not None else w_local.B
     wide = (n_seqs * w.H <= torch.cuda.get_device_properties(dev).multi_processor_count
             and not os.environ.get("FKDA_TC_NO_WIDE"))
     names = {"twopass": ("fkda::prepare_warp_kernel", "fkda::recurrence_kernel")}.get(
-        algo, ("fkda::prepare_warp_kernel", "fkda::recurrence_tc_wide_kernel" if wide else "fkda::recurrence_tc_kernel"))
+        algo, ("fkda::prepare_warp_kernel", "fkda::recurrence_tc_wide_kernel" if wide else
+               ("fkda::recurrence_tc_kernel" if os.environ.get("FKDA_TC_SS") else "fkda::recurrence_tc_ts_kernel")))
     kernel_times = {}
     n_phase = 3
     barrier()

@@ -1,16 +1,22 @@
-// Tensor-core recurrence with the state's MMA copy in TENSOR MEMORY instead of shared memory.
+// Tensor-core recurrence with every tcgen05.mma A operand in TENSOR MEMORY (the default kernel when there are
+// more chains than SMs).
 //
-// Same chunk walk, records, numerics and scheduling as recurrence_tc_kernel; what changes is where the
-// bf16 state lives between chunks and the orientation of the state update:
+// Same chunk walk, records, numerics and scheduling as recurrence_tc_kernel (fkda_tc.cu); what changes is where
+// the operands live and the orientation of the state update:
 //   * thread v (= TMEM lane v) owns state ROW v, S[v, 0..127], in 64 packed registers (k pairs);
 //   * the copy that the first product of a chunk reads, D1[V,32] = S[V,K] . [kd; qd]^T, is the A operand
 //     of tcgen05.mma in tensor memory (lane = v, 64 columns of bf16 pairs), written with tcgen05.st by
 //     the owner threads: no 32 KB shared-memory tile is written and re-read per chunk;
-//   * the update product is DST[V,K] = U^T[V,16] . kr[16,K] (A = the U tile in shared memory, B = the kr
-//     tile read N-major), so thread v reads DST[v, :] from its own lane and applies
-//     S[v,k] = bf(fma(S[v,k], E_tot[k], DST[v,k])) with E_tot broadcast from the record in shared memory;
+//   * the A operands of the 16-deep products, u'^T and U^T ([V, 16 tokens] = 8 columns of bf16 pairs), are
+//     written to tensor memory by the threads that form them as well: no shared-memory operand tile and no
+//     generic-to-async proxy fence between the element-wise steps and the next MMA;
+//   * the update product is DST[V,K] = U^T[V,16] . kr[16,K] (B = the kr tile read N-major), so thread v reads
+//     DST[v, :] from its own lane and applies S[v,k] = bf(fma(S[v,k], E_tot[k], DST[v,k])) with E_tot
+//     broadcast from the record in shared memory;
 //   * the state copy aliases the first 64 of the 128 DST columns: it is dead once D1 is complete, and
 //     the update writes pairs 8b..8b+7 only after DST columns 16b..16b+15 have been read.
+// Tensor memory per chain: DST 128 + D1 32 + A 8 columns; 504 of 512 with three chains.  Shared memory holds only
+// what TMA moves: two record stages, two value tiles, one out tile per chain.
 // Included by fkda_tc.cu.
 #pragma once
 
