@@ -665,7 +665,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     if (do_rec && (!encode_token_map(&maps.v, p.v, p.B * p.T, p.H, p.token_stride) ||
                    !encode_token_map(&maps.out, p.out, p.B * p.T, p.H, p.token_stride)))
         return FKDA_ERR_LAUNCH;
-    const int wide_smem = kSmChainBytes + (int)sizeof(TcWideCtrl) + 128;
+    const int wide_smem = kWideCtrlOff + (int)sizeof(TcWideCtrl) + 128;
     if (do_rec && wide &&
         cudaFuncSetAttribute(recurrence_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem) != cudaSuccess)
         return FKDA_ERR_LAUNCH;

@@ -38,6 +38,8 @@ __device__ __forceinline__ void wide_update(uint32_t (&sreg)[64], uint32_t t_ds_
     }
 }
 
+constexpr int kWideOut = kSmChainBytes;            // 2 x [16][128] bf16
+constexpr int kWideCtrlOff = kWideOut + 2 * 4096;
 struct TcWideCtrl {
     uint64_t full[kTcStages];
     uint64_t mma;    // completion of MMA1 and MMA2 (warpgroup 0 only)
@@ -50,7 +52,9 @@ __global__ void __launch_bounds__(384, 1)
 recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constant__ TcMaps maps) {
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* cs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
-    TcWideCtrl& ctl = *reinterpret_cast<TcWideCtrl*>(cs + kSmChainBytes);
+    // after the chain block: two out tiles (a TMA store reads one while the next chunk's is formed), then the
+    // control block
+    TcWideCtrl& ctl = *reinterpret_cast<TcWideCtrl*>(cs + kWideCtrlOff);
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int wg = warp >> 2;          // 0: runs the chunk; 1, 2: state-update helpers
@@ -146,13 +150,13 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                     make_uint4(sreg[4 * vg], sreg[4 * vg + 1], sreg[4 * vg + 2], sreg[4 * vg + 3]);
         fence_proxy_async_smem();
         named_barrier_sync(kBarAll, 384);
-        __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kSmOut);
 
         for (int t = c0; t < c1; ++t) {
             const int s = t % kTcStages;
             uint8_t* st = cs + kSmStage + s * kSmStageBytes;
             const uint32_t st_addr = smem_u32(st);
             const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk);
+            __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kWideOut + (t & 1) * 4096);
 
             // ---- operands of chunk t have landed (every warpgroup observes it: the helpers read E_tot) ----
             if (!mbar_wait_bounded(&ctl.full[s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
@@ -161,7 +165,6 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
                 if (wiw == 0) {
                     if (elect_one()) {
-                        bulk_wait_group_read<0>();  // the previous out tile (shares the A23 tile) has been read
                         tc_fence_after_sync();
                         const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, kTcB1Lbo, 128);
 #pragma unroll
@@ -228,11 +231,18 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
             if (wg == 0) wide_update<0, 2>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
             else if (wg == 1) wide_update<2, 5>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
             else wide_update<5, 8>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
+            // warp 4 issues the TMA store and the refill, so that warpgroup 0 can go straight to the next chunk's MMA;
+            // before the barrier it makes sure the store of the previous chunk has read its out tile (the one the
+            // next chunk will overwrite)
+            if (warp == 4) {
+                if (elect_one()) bulk_wait_group_read<0>();
+                __syncwarp();
+            }
             fence_proxy_async_smem();
             tc_fence_before_sync();
             named_barrier_sync(kBarAll, 384);
             // ---- store the out tile, refill the stage just consumed ----
-            if (warp == 0) {
+            if (warp == 4) {
                 if (elect_one()) {
                     if (len == kChunk) {
                         tma_store_3d(&maps.out, 0, h, (int)(bos + (int64_t)t * kChunk), out_tile);
