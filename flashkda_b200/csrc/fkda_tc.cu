@@ -533,8 +533,8 @@ recurrence_tc_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constan
 
 }  // namespace fkda
 
-#include "fkda_tc_wide.cuh"
 #include "fkda_tc_ts.cuh"
+#include "fkda_tc_wide.cuh"
 
 namespace fkda {
 

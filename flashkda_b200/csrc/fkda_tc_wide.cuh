@@ -1,44 +1,45 @@
 // "Wide" variant of the tensor-core recurrence for the few-chains regime (no more chains than SMs):
 // ONE chain per CTA, and the two warpgroups that would otherwise idle help with the largest
-// element-wise step of a chunk, the state update.  Warpgroup 0 runs the chunk exactly as in
-// recurrence_tc_kernel (MMA issue, u', U, out); the 128 rows v of the transposed state update
-// DST[k, v] are split in three ranges, one per warpgroup (thread k of warpgroup j owns S[v, k] for v
-// in its range, in registers).  Same numerics, same record format, same TMEM / shared-memory layout
-// (chain block 0 only).  Included by fkda_tc.cu.
+// element-wise step of a chunk, the state update.  Warpgroup 0 runs the chunk as in
+// recurrence_tc_ts_kernel (MMA issue, u', U, out; every A operand in tensor memory); the 128 columns k of
+// the state update DST[v, k] are split in three ranges, one per warpgroup (thread v of warpgroup j owns
+// S[v, k] for k in its range, in registers, and writes the refreshed pairs to the tensor-memory copy that the
+// next chunk's first MMA reads).  Same numerics and record format.  Included by fkda_tc.cu.
 #pragma once
 
 namespace fkda {
 
-// rows v = 16*b .. 16*b+15 of the state are "batch" b; batches [lo, hi) per warpgroup
+// columns k = 16*b .. 16*b+15 of the state are "batch" b; batches [lo, hi) per warpgroup
 // (warpgroup 0 also forms the out tile, so it gets the smallest share)
 __device__ __forceinline__ int wide_batch_lo(int wg) { return wg == 0 ? 0 : (wg == 1 ? 2 : 5); }
 __device__ __forceinline__ int wide_batch_hi(int wg) { return wg == 0 ? 2 : (wg == 1 ? 5 : 8); }
 
-// State update of batches [kLo, kHi) of column k: S[vv][k] = bf(fma(S[vv][k], E_tot[k], DST[k][vv])) in
-// registers, and the refreshed rows into the S^T tile.
+// State update of batches [kLo, kHi) of row v: S[v][k] = bf(fma(S[v][k], E_tot[k], DST[v][k])) in registers,
+// and the refreshed pairs into the tensor-memory state copy.
 template <int kLo, int kHi>
-__device__ __forceinline__ void wide_update(uint32_t (&sreg)[64], uint32_t t_ds_lane, float e_mine, uint8_t* s_tile,
-                                            int k) {
+__device__ __forceinline__ void wide_update(uint32_t (&sreg)[64], uint32_t t_ds_lane, uint32_t t_s_lane, const float4* et4) {
 #pragma unroll
     for (int b = kLo; b < kHi; ++b) {
         uint32_t r[16];
         sm100::tmem_ld16(t_ds_lane + 16 * b, r);
         sm100::tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t sv = sreg[8 * b + i];
-            sreg[8 * b + i] = pack_bf2(__fmaf_rn(bf_lo(sv), e_mine, __uint_as_float(r[2 * i])),
-                                       __fmaf_rn(bf_hi(sv), e_mine, __uint_as_float(r[2 * i + 1])));
+        for (int q = 0; q < 4; ++q) {
+            const float4 e = et4[4 * b + q];  // same address in every lane: one broadcast read
+            const uint32_t s0 = sreg[8 * b + 2 * q], s1 = sreg[8 * b + 2 * q + 1];
+            sreg[8 * b + 2 * q] = pack_bf2(__fmaf_rn(bf_lo(s0), e.x, __uint_as_float(r[4 * q])),
+                                           __fmaf_rn(bf_hi(s0), e.y, __uint_as_float(r[4 * q + 1])));
+            sreg[8 * b + 2 * q + 1] = pack_bf2(__fmaf_rn(bf_lo(s1), e.z, __uint_as_float(r[4 * q + 2])),
+                                               __fmaf_rn(bf_hi(s1), e.w, __uint_as_float(r[4 * q + 3])));
         }
-#pragma unroll
-        for (int q = 0; q < 2; ++q)
-            *reinterpret_cast<uint4*>(s_tile + sT_off(k, 2 * b + q)) =
-                make_uint4(sreg[8 * b + 4 * q], sreg[8 * b + 4 * q + 1], sreg[8 * b + 4 * q + 2],
-                           sreg[8 * b + 4 * q + 3]);
+        sm100::tmem_st8(t_s_lane + 8 * b, sreg[8 * b], sreg[8 * b + 1], sreg[8 * b + 2], sreg[8 * b + 3],
+                        sreg[8 * b + 4], sreg[8 * b + 5], sreg[8 * b + 6], sreg[8 * b + 7]);
     }
 }
 
-constexpr int kWideOut = kSmChainBytes;            // 2 x [16][128] bf16
+// shared memory of the one chain: record stages and value tiles as in fkda_tc_ts.cuh, then two out tiles (a TMA
+// store reads one while the next chunk's is formed), then the control block
+constexpr int kWideOut = kTsOut;                   // 2 x [16][128] bf16
 constexpr int kWideCtrlOff = kWideOut + 2 * 4096;
 struct TcWideCtrl {
     uint64_t full[kTcStages];
@@ -52,14 +53,12 @@ __global__ void __launch_bounds__(384, 1)
 recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constant__ TcMaps maps) {
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* cs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
-    // after the chain block: two out tiles (a TMA store reads one while the next chunk's is formed), then the
-    // control block
     TcWideCtrl& ctl = *reinterpret_cast<TcWideCtrl*>(cs + kWideCtrlOff);
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int wg = warp >> 2;          // 0: runs the chunk; 1, 2: state-update helpers
     const int wiw = warp & 3;
-    const int v = threadIdx.x & 127;   // TMEM lane: V row (D1..D3) / state column k (DST)
+    const int v = threadIdx.x & 127;   // TMEM lane = V row = state row
     const int b_lo = wide_batch_lo(wg), b_hi = wide_batch_hi(wg);
     volatile int* abort_flag = &ctl.abort_flag;
 
@@ -82,12 +81,12 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_ds = tmem_base;          // DST (128 columns; D2 in its first 16)
     const uint32_t t_d1 = tmem_base + 128u;   // u0 | o0, later D3 | o0
+    const uint32_t t_s = tmem_base + 160u;    // bf16 state copy, 64 columns of k pairs (A operand of MMA1)
+    const uint32_t t_a = tmem_base + 224u;    // u'^T, then U^T: 8 columns of token pairs (A operand of MMA2, MMA3)
 
-    constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, true, false);
+    constexpr uint32_t idesc_n32 = make_idesc_bf16_f32(128, 32, false, false);
     constexpr uint32_t idesc_n16 = make_idesc_bf16_f32(128, 16, false, false);
-    constexpr uint32_t idesc_dst = make_idesc_bf16_f32(128, 128, true, false);
-    const uint64_t s_desc0 = make_smem_desc(smem_u32(cs + kSmS), 2048, 128);
-    const uint64_t a23_desc = make_smem_desc(smem_u32(cs + kSmA23), 2048, 128);
+    constexpr uint32_t idesc_dst = make_idesc_bf16_f32(128, 128, false, true);   // B = kr tile, N-major
     constexpr int kBarMain = 1, kBarAll = 2;
     const int64_t n_chains = a.N * a.H;
     uint32_t full_phase[kTcStages] = {0, 0};
@@ -99,7 +98,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         const int64_t n = ch.n, bos = ch.bos, seq_len = ch.seq_len;
         const int h = ch.h, n_chunks = ch.n_chunks;
         const uint8_t* rec_base = ch.rec_base;
-        const int64_t st_base = (n * a.H + h) * (int64_t)(kD * kD) + v;  // S[vv][k = v] at st_base + vv * 128
+        const int64_t st_base = ((n * a.H + h) * (int64_t)kD + v) * (int64_t)kD;  // S[v][k] at st_base + k
         // chunk range of this launch: all chunks, or one slab of a pipelined forward (fixed batches)
         const int c0 = a.slab_chunks > 0 ? a.slab_c0 : 0;
         const int c1 = (a.slab_chunks > 0 && c0 + a.slab_chunks < n_chunks) ? c0 + a.slab_chunks : n_chunks;
@@ -108,8 +107,8 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         auto issue_load = [&](int t) {
             const int s = t % kTcStages;
             mbar_arrive_expect_tx(&ctl.full[s], (uint32_t)(kTcRecord + kChunk * kD * 2));
-            bulk_g2s(cs + kSmStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[s]);
-            tma_load_3d(cs + kSmV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[s]);
+            bulk_g2s(cs + kTsStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[s]);
+            tma_load_3d(cs + kTsV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[s]);
         };
         if (threadIdx.x == 0) {
             for (int t = c0; t < c0 + kTcStages && t < c1; ++t) issue_load(t);
@@ -117,7 +116,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         const int64_t tstride = a.token_stride;
         unsigned short* ocol = reinterpret_cast<unsigned short*>(a.out) + bos * tstride + (int64_t)h * kD + v;
 
-        // ---- initial state: my rows of column k into registers (pairs over v) and into the S^T tile ----
+        // ---- initial state: my columns of row v into registers (pairs over k) and into the tensor-memory copy ----
         uint32_t sreg[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) sreg[i] = 0u;
@@ -131,29 +130,32 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
             }
         } else if (a.initial_state != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                if ((i >> 3) >= b_lo && (i >> 3) < b_hi) {
+            for (int i = 0; i < 16; ++i) {   // group i = state columns 8i .. 8i+7 = registers 4i .. 4i+3
+                if ((i >> 1) >= b_lo && (i >> 1) < b_hi) {
                     if (a.state_fp32) {
-                        const float* src = reinterpret_cast<const float*>(a.initial_state) + st_base;
-                        sreg[i] = pack_bf2(src[(2 * i) * kD], src[(2 * i + 1) * kD]);
+                        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.initial_state) + st_base) + 2 * i;
+                        const float4 x = src[0], y = src[1];
+                        sreg[4 * i] = pack_bf2(x.x, x.y); sreg[4 * i + 1] = pack_bf2(x.z, x.w);
+                        sreg[4 * i + 2] = pack_bf2(y.x, y.y); sreg[4 * i + 3] = pack_bf2(y.z, y.w);
                     } else {
-                        const unsigned short* src = reinterpret_cast<const unsigned short*>(a.initial_state) + st_base;
-                        sreg[i] = (uint32_t)src[(2 * i) * kD] | ((uint32_t)src[(2 * i + 1) * kD] << 16);
+                        const uint4 x = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(a.initial_state) + st_base)[i];
+                        sreg[4 * i] = x.x; sreg[4 * i + 1] = x.y; sreg[4 * i + 2] = x.z; sreg[4 * i + 3] = x.w;
                     }
                 }
             }
         }
 #pragma unroll
-        for (int vg = 0; vg < 16; ++vg)
-            if ((vg >> 1) >= b_lo && (vg >> 1) < b_hi)
-                *reinterpret_cast<uint4*>(cs + kSmS + sT_off(v, vg)) =
-                    make_uint4(sreg[4 * vg], sreg[4 * vg + 1], sreg[4 * vg + 2], sreg[4 * vg + 3]);
-        fence_proxy_async_smem();
+        for (int b = 0; b < 8; ++b)
+            if (b >= b_lo && b < b_hi)
+                tmem_st8(t_s + 8 * b + lane_sel, sreg[8 * b], sreg[8 * b + 1], sreg[8 * b + 2], sreg[8 * b + 3],
+                         sreg[8 * b + 4], sreg[8 * b + 5], sreg[8 * b + 6], sreg[8 * b + 7]);
+        tmem_wait_st();
+        tc_fence_before_sync();
         named_barrier_sync(kBarAll, 384);
 
         for (int t = c0; t < c1; ++t) {
             const int s = t % kTcStages;
-            uint8_t* st = cs + kSmStage + s * kSmStageBytes;
+            uint8_t* st = cs + kTsStage + s * kSmStageBytes;
             const uint32_t st_addr = smem_u32(st);
             const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk);
             __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kWideOut + (t & 1) * 4096);
@@ -169,29 +171,40 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                         const uint64_t bd0 = make_smem_desc(st_addr + kTcB1, kTcB1Lbo, 128);
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            umma_ss(t_d1, s_desc0 + (uint64_t)(j * 256), bd0 + (uint64_t)(j * (2 * kTcB1Lbo / 16)),
-                                    idesc_n32, j > 0 ? 1u : 0u);
+                            umma_ts(t_d1, t_s + 8u * j, bd0 + (uint64_t)(j * (2 * kTcB1Lbo / 16)), idesc_n32, j > 0 ? 1u : 0u);
                         umma_commit(&ctl.mma);
                     }
                     __syncwarp();
                 }
                 unsigned short v_cur[kChunk];  // value column v of this chunk (zero past the sequence end)
-                tc_load_v_column(cs + kSmV + s * 4096, v, len, v_cur);
+                tc_load_v_column(cs + kTsV + s * 4096, v, len, v_cur);
                 uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta)
                 tc_load_beta(st, bpk);
                 if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
                 mma_phase ^= 1u;
                 tc_fence_after_sync();
                 // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
-                tc_form_u_prime(t_d1 + lane_sel, cs + kSmA23, v, v_cur, bpk);
-                fence_proxy_async_smem();
+                {
+                    uint32_t r[16];
+                    tmem_ld16(t_d1 + lane_sel, r);
+                    tmem_wait_ld();
+                    uint32_t up[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t u0 = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                        const uint32_t vp = (uint32_t)v_cur[2 * i] | ((uint32_t)v_cur[2 * i + 1] << 16);
+                        up[i] = bf2_mul(bf2_sub(vp, u0), bpk[i]);
+                    }
+                    tmem_st8(t_a + lane_sel, up[0], up[1], up[2], up[3], up[4], up[5], up[6], up[7]);
+                    tmem_wait_st();
+                }
                 tc_fence_before_sync();
                 named_barrier_sync(kBarMain, 128);
                 // ---- MMA2: D2[V,16] = u'^T . INV^T  (into the first 16 DST columns) ----
                 if (wiw == 0) {
                     if (elect_one()) {
                         tc_fence_after_sync();
-                        umma_ss(t_ds, a23_desc, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
+                        umma_ts(t_ds, t_a, make_smem_desc(st_addr + kTcInv, 256, 128), idesc_n16, 0u);
                         umma_commit(&ctl.mma);
                     }
                     __syncwarp();
@@ -199,16 +212,24 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
                 mma_phase ^= 1u;
                 tc_fence_after_sync();
-                tc_form_u(t_ds + lane_sel, cs + kSmA23, v);  // U = bf(D2)
-                fence_proxy_async_smem();
+                {   // U = bf(D2) replaces u' as the A operand
+                    uint32_t r[16];
+                    tmem_ld16(t_ds + lane_sel, r);
+                    tmem_wait_ld();
+                    uint32_t p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) p[i] = pack_bf2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    tmem_st8(t_a + lane_sel, p[0], p[1], p[2], p[3], p[4], p[5], p[6], p[7]);
+                    tmem_wait_st();
+                }
                 tc_fence_before_sync();
                 named_barrier_sync(kBarMain, 128);
-                // ---- MMA3: D3[V,16] = U^T . Mqk^T (over the dead u0 columns);  DST[K,V] = kr^T . U ----
+                // ---- MMA3: D3[V,16] = U^T . Mqk^T (over the dead u0 columns);  DST[V,K] = U^T . kr ----
                 if (wiw == 0) {
                     if (elect_one()) {
                         tc_fence_after_sync();
-                        umma_ss(t_d1, a23_desc, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
-                        umma_ss(t_ds, make_smem_desc(st_addr + kTcKr, kTcKrLbo, kTcKrSbo), a23_desc, idesc_dst, 0u);
+                        umma_ts(t_d1, t_a, make_smem_desc(st_addr + kTcMqk, 256, 128), idesc_n16, 0u);
+                        umma_ts(t_ds, t_a, make_smem_desc(st_addr + kTcKr, kTcKrLbo, kTcKrSbo), idesc_dst, 0u);
                         umma_commit(&ctl.mma3);
                     }
                     __syncwarp();
@@ -218,7 +239,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
             if (!mbar_wait_bounded(&ctl.mma3, mma3_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
             mma3_phase ^= 1u;
             tc_fence_after_sync();
-            const float e_mine = reinterpret_cast<const float*>(st + kTcEt)[v];  // gate decay of my state column
+            const float4* et4 = reinterpret_cast<const float4*>(st + kTcEt);  // gate decay of the 128 state columns
 
             if (wg == 0) {
                 // ---- out = bf(o0) (+) bf(Mqk U) (thread = V row) ----
@@ -227,10 +248,11 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 tmem_wait_ld();
                 tc_store_out(r, reinterpret_cast<unsigned short*>(out_tile), ocol + (int64_t)t * kChunk * tstride, tstride, v, len);
             }
-            // ---- my rows of state column k ----
-            if (wg == 0) wide_update<0, 2>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
-            else if (wg == 1) wide_update<2, 5>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
-            else wide_update<5, 8>(sreg, t_ds + lane_sel, e_mine, cs + kSmS, v);
+            // ---- my columns of state row v ----
+            if (wg == 0) wide_update<0, 2>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
+            else if (wg == 1) wide_update<2, 5>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
+            else wide_update<5, 8>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
+            tmem_wait_st();
             // warp 4 issues the TMA store and the refill, so that warpgroup 0 can go straight to the next chunk's MMA;
             // before the barrier it makes sure the store of the previous chunk has read its out tile (the one the
             // next chunk will overwrite)
@@ -260,18 +282,17 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 if ((i >> 1) >= b_lo && (i >> 1) < b_hi)
                     seg_mine[i * 128] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
         } else if (a.final_state != nullptr) {
-            // ---- final state: my rows of my column, bf16 or widened to fp32 ----
+            // ---- final state: my columns of my row, bf16 or widened to fp32 ----
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                if ((i >> 3) >= b_lo && (i >> 3) < b_hi) {
+            for (int i = 0; i < 16; ++i) {
+                if ((i >> 1) >= b_lo && (i >> 1) < b_hi) {
                     if (a.state_fp32) {
-                        float* dst = reinterpret_cast<float*>(a.final_state) + st_base;
-                        dst[(2 * i) * kD] = bf_lo(sreg[i]);
-                        dst[(2 * i + 1) * kD] = bf_hi(sreg[i]);
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.final_state) + st_base) + 2 * i;
+                        dst[0] = make_float4(bf_lo(sreg[4 * i]), bf_hi(sreg[4 * i]), bf_lo(sreg[4 * i + 1]), bf_hi(sreg[4 * i + 1]));
+                        dst[1] = make_float4(bf_lo(sreg[4 * i + 2]), bf_hi(sreg[4 * i + 2]), bf_lo(sreg[4 * i + 3]), bf_hi(sreg[4 * i + 3]));
                     } else {
-                        unsigned short* dst = reinterpret_cast<unsigned short*>(a.final_state) + st_base;
-                        dst[(2 * i) * kD] = (unsigned short)(sreg[i] & 0xffffu);
-                        dst[(2 * i + 1) * kD] = (unsigned short)(sreg[i] >> 16);
+                        reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.final_state) + st_base)[i] =
+                            make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
                     }
                 }
             }
