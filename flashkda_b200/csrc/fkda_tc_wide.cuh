@@ -11,8 +11,8 @@ namespace fkda {
 
 // columns k = 16*b .. 16*b+15 of the state are "batch" b; batches [lo, hi) per warpgroup
 // (warpgroup 0 also forms the out tile, so it gets the smallest share)
-__device__ __forceinline__ int wide_batch_lo(int wg) { return wg == 0 ? 0 : (wg == 1 ? 2 : 5); }
-__device__ __forceinline__ int wide_batch_hi(int wg) { return wg == 0 ? 2 : (wg == 1 ? 5 : 8); }
+__device__ __forceinline__ int wide_batch_lo(int wg) { return wg == 0 ? 0 : (wg == 1 ? 1 : 4); }
+__device__ __forceinline__ int wide_batch_hi(int wg) { return wg == 0 ? 1 : (wg == 1 ? 4 : 8); }
 
 // State update of batches [kLo, kHi) of row v: S[v][k] = bf(fma(S[v][k], E_tot[k], DST[v][k])) in registers,
 // and the refreshed pairs into the tensor-memory state copy.
@@ -249,9 +249,9 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 tc_store_out(r, reinterpret_cast<unsigned short*>(out_tile), ocol + (int64_t)t * kChunk * tstride, tstride, v, len);
             }
             // ---- my columns of state row v ----
-            if (wg == 0) wide_update<0, 2>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
-            else if (wg == 1) wide_update<2, 5>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
-            else wide_update<5, 8>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
+            if (wg == 0) wide_update<0, 1>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
+            else if (wg == 1) wide_update<1, 4>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
+            else wide_update<4, 8>(sreg, t_ds + lane_sel, t_s + lane_sel, et4);
             tmem_wait_st();
             // warp 4 issues the TMA store and the refill, so that warpgroup 0 can go straight to the next chunk's MMA;
             // before the barrier it makes sure the store of the previous chunk has read its out tile (the one the
