@@ -679,24 +679,38 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     if (wide && !varlen && p.phase_mask == 0 && idle_sms >= 32 && tps >= 64 && getenv("FKDA_TC_NO_SLABS") == nullptr) {
         SlabStreams* ss = slab_streams(dev);
         if (ss == nullptr) return FKDA_ERR_LAUNCH;
+        // Slab boundaries.  The prepare of slab i+1 (on idle_sms SMs, about 5.2 ns per (chunk, head) on the whole
+        // GPU) must be done when the recurrence (about 1.18 us per chunk) has walked slab i.  When prepare is at
+        // least twice as fast (x <= 0.5) the slabs grow, 1/8, 1/4, 5/16, 5/16 of the chunks (1/3, 2/3 for two), so
+        // that little prepare work goes first, unhidden; otherwise they are equal.
         const int n_slabs = tps >= 256 ? kMaxSlabs : 2;
-        const int slab_len = (int)(((tps + n_slabs - 1) / n_slabs + 1) / 2 * 2);  // even
+        const double x = (double)chains * (double)sms / ((double)idle_sms * 227.0);
+        static const double grow4[kMaxSlabs + 1] = {0.0, 0.125, 0.375, 0.6875, 1.0}, grow2[3] = {0.0, 1.0 / 3.0, 1.0};
+        int bounds[kMaxSlabs + 1];
+        for (int i = 0; i <= n_slabs; ++i) {
+            const double frac = x <= 0.5 ? (n_slabs == 2 ? grow2[i] : grow4[i]) : (double)i / n_slabs;
+            bounds[i] = (int)((int64_t)(frac * (double)tps + 1.0) / 2 * 2);  // even
+        }
+        bounds[0] = 0;
+        bounds[n_slabs] = (int)tps;
         auto slab_args = [&](int i) {
             TwoPassArgs x = a;
-            x.slab_c0 = i * slab_len;
-            x.slab_chunks = (int)((int64_t)x.slab_c0 + slab_len <= tps ? slab_len : tps - x.slab_c0);
+            x.slab_c0 = bounds[i];
+            x.slab_chunks = bounds[i + 1] - bounds[i];
             return x;
         };
         if (launch_prepare_warp<true>(slab_args(0), stream) != FKDA_OK) return FKDA_ERR_LAUNCH;
         ++launches;
         if (cudaEventRecord(ss->fork, stream) != cudaSuccess || cudaStreamWaitEvent(ss->side, ss->fork, 0) != cudaSuccess)
             return FKDA_ERR_LAUNCH;
-        for (int i = 1; i < n_slabs && (int64_t)i * slab_len < tps; ++i) {
+        for (int i = 1; i < n_slabs; ++i) {
+            if (bounds[i + 1] <= bounds[i]) continue;
             if (launch_prepare_warp<true>(slab_args(i), ss->side, idle_sms) != FKDA_OK) return FKDA_ERR_LAUNCH;
             ++launches;
             if (cudaEventRecord(ss->done[i], ss->side) != cudaSuccess) return FKDA_ERR_LAUNCH;
         }
-        for (int i = 0; i < n_slabs && (int64_t)i * slab_len < tps; ++i) {
+        for (int i = 0; i < n_slabs; ++i) {
+            if (bounds[i + 1] <= bounds[i]) continue;
             if (i > 0 && cudaStreamWaitEvent(stream, ss->done[i], 0) != cudaSuccess) return FKDA_ERR_LAUNCH;
             recurrence_tc_wide_kernel<<<(unsigned)chains, 384, wide_smem, stream>>>(slab_args(i), maps);
             ++launches;
