@@ -15,9 +15,11 @@
 //   * the other element-wise steps (bf16 roundings, beta) by the same 128 threads in the other
 //     orientation (thread v = TMEM lane v of D1/D2/D3), reading accumulators with tcgen05.ld.
 // Three independent chains run per CTA (one warpgroup each) so that the tensor-core / barrier latency
-// of one chain is covered by the element-wise work of the others.  Two variants live in their own files:
-// fkda_tc_wide.cuh (one chain per CTA, for no more chains than SMs) and fkda_tc_ts.cuh (the state's MMA copy
-// in tensor memory instead of shared memory, opt-in); the helpers below are shared by all three.
+// of one chain is covered by the element-wise work of the others.
+// The kernel of THIS file keeps the state copy and the 16-deep operands in shared memory; it is the
+// FKDA_TC_SS=1 variant.  The default kernels live in their own files and share the helpers below:
+// fkda_tc_ts.cuh (the same walk with every A operand in tensor memory: default for more chains than SMs) and
+// fkda_tc_wide.cuh (one chain per CTA, for no more chains than SMs).
 //
 // Numerics: steps B1-B7 of the reference's contract (tests/torch_ref.py:231-251; the reference's own
 // recurrence is csrc/smxx/fwd_kernel2.cuh:434-742, built on mma.sync with register transposes).
