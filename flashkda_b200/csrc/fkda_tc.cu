@@ -582,6 +582,7 @@ static size_t seg_state_bytes(int64_t H, int64_t N) { return (size_t)(H * N) * 3
 // Side stream and events of the slab pipeline, one set per device, created on first use.
 constexpr int kMaxSlabs = 4;
 struct SlabStreams {
+    std::mutex launch_mu;  // one slab pipeline at a time is ENQUEUED per device (event record / wait pairs stay paired)
     cudaStream_t side = nullptr;
     cudaEvent_t fork = nullptr, done[kMaxSlabs] = {nullptr, nullptr, nullptr, nullptr};
     bool ready = false;
@@ -681,6 +682,8 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     if (wide && !varlen && p.phase_mask == 0 && idle_sms >= 32 && tps >= 64 && getenv("FKDA_TC_NO_SLABS") == nullptr) {
         SlabStreams* ss = slab_streams(dev);
         if (ss == nullptr) return FKDA_ERR_LAUNCH;
+        // host threads that call concurrently on one device share the side stream and its events
+        std::lock_guard<std::mutex> enqueue_lock(ss->launch_mu);
         // Slab boundaries.  The prepare of slab i+1 (on idle_sms SMs, about 5.2 ns per (chunk, head) on the whole
         // GPU) must be done when the recurrence (about 1.18 us per chunk) has walked slab i.  When prepare is at
         // least twice as fast (x <= 0.5) the slabs grow, 1/8, 1/4, 5/16, 5/16 of the chunks (1/3, 2/3 for two), so

@@ -317,3 +317,49 @@ def test_slab_pipeline_matches_single_pass(B, T, H, monkeypatch):
     if T <= 2100:
         ref_out, ref_hT = run_oracle(inp)
         check_against(out_p, hT_p, ref_out, ref_hT)
+
+
+def test_concurrent_host_threads_share_the_slab_pipeline():
+    """Two host threads run slab-pipelined forwards at the same time on their own CUDA streams and workspaces;
+    they share the device's side stream and events, and each must get the result of a lone call."""
+    import threading
+    problems = []
+    for seed in (41, 42):
+        w = Workload("thr", 1, 4096, 8, state_in="fp32", state_out="fp32", lower_bound=-1.0)
+        d = to_device(make_inputs(w, seed=seed), "cuda")
+        ws = torch.empty(flashkda_b200.get_workspace_size(w.tokens, w.H, 1), dtype=torch.uint8, device="cuda")
+        problems.append((d, ws))
+
+    def call(d, ws, out, hT):
+        flashkda_b200.fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], out, A_log=d["A_log"],
+                          dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], initial_state=d["initial_state"],
+                          final_state=hT, workspace=ws)
+
+    refs = []
+    for d, ws in problems:
+        out, hT = torch.zeros_like(d["v"]), torch.zeros_like(d["final_state"])
+        call(d, ws, out, hT)
+        torch.cuda.synchronize()
+        refs.append((out, hT))
+    results = [None, None]
+
+    def worker(i):
+        d, ws = problems[i]
+        stream = torch.cuda.Stream()
+        outs = []
+        with torch.cuda.stream(stream):
+            for _ in range(20):
+                out, hT = torch.zeros_like(d["v"]), torch.zeros_like(d["final_state"])
+                call(d, ws, out, hT)
+                outs.append((out, hT))
+        stream.synchronize()
+        results[i] = outs
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(2):
+        for out, hT in results[i]:
+            assert torch.equal(out, refs[i][0]) and torch.equal(hT, refs[i][1])
