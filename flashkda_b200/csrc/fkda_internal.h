@@ -19,6 +19,7 @@ struct TwoPassArgs {
     void* final_state;
     const int64_t* cu_seqlens;
     int32_t* tile_prefix;  // [N + 1] chunk-count prefix (varlen only)
+    const int32_t* seq_order;  // [N] sequences by decreasing length (varlen with N <= kSeqOrderMaxN, else nullptr)
     uint8_t* workspace;    // [H][total_tiles] per-chunk records
     int32_t* queue;        // header word 0: ticket counter of the persistent recurrence (zeroed per call)
     int32_t* status;       // header word 1: device status, 0 ok, else the code of a bounded wait that gave up
@@ -40,7 +41,9 @@ struct TwoPassArgs {
 //   [256, ..) tile prefix (N + 1 int32, padded to 256 B)
 //   then      H * total_tiles records
 constexpr size_t kWsHeaderBytes = 256;
-inline size_t ws_prefix_bytes(int64_t N) { return (size_t)(((N + 1) * 4 + 255) / 256 * 256); }
+// (N + 1) prefix entries followed by N entries of the length order
+inline size_t ws_prefix_bytes(int64_t N) { return (size_t)(((2 * N + 1) * 4 + 255) / 256 * 256); }
+constexpr int64_t kSeqOrderMaxN = 512;  // beyond this the quadratic ranking in the prefix kernel is not worth its time
 inline int64_t ws_tiles_upper_bound(int64_t T_total, int64_t N) { return (T_total + 15) / 16 + N; }
 
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
@@ -54,6 +57,6 @@ int launch_decode(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches
 // Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
 // workspace carving).
 void fill_args(const fkda_fwd_params& p, TwoPassArgs* a);
-void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, cudaStream_t stream);
+void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, cudaStream_t stream);
 
 }  // namespace fkda

@@ -95,8 +95,9 @@ struct TcChain {
 };
 __device__ __forceinline__ TcChain tc_locate_chain(const TwoPassArgs& a, int64_t chain) {
     TcChain c;
-    c.n = chain / a.H;
-    c.h = (int)(chain - c.n * a.H);
+    const int64_t s = chain / a.H;  // position in the order the chains are started in
+    c.h = (int)(chain - s * a.H);
+    c.n = a.seq_order != nullptr ? a.seq_order[s] : s;
     int64_t tile_base;
     if (a.cu_seqlens != nullptr) {
         c.bos = a.cu_seqlens[c.n];
@@ -122,7 +123,10 @@ __device__ __forceinline__ TcChain tc_locate_chain(const TwoPassArgs& a, int64_t
 // Returns the item, -2 when all chains are finished, -3 when the bounded wait gave up.
 __device__ __forceinline__ int tc_next_item(const TwoPassArgs& a, bool first_ticket, int wg, int64_t n_chains,
                                             volatile int* abort_flag) {
-    const int ticket = first_ticket ? wg * (int)gridDim.x + (int)blockIdx.x
+    // (odd layers run backwards over the CTAs: with chains ordered by decreasing length the longest chains of one
+    //  layer meet the shortest of the next)
+    const int cta = (wg & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    const int ticket = first_ticket ? wg * (int)gridDim.x + cta
                                     : kTcChains * (int)gridDim.x + atomicAdd(a.queue, 1);
     if (ticket < n_chains) return ticket;
     int item = -2;
@@ -726,7 +730,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     }
 
     if (varlen && do_prep) {
-        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, stream);
+        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order), stream);
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {

@@ -17,8 +17,10 @@ namespace fkda {
 // varlen: chunk-count prefix over the sequences, tile_prefix[n] = sum_{m<n} ceil(len_m/16)
 // (replaces the reference's single-thread loop, csrc/smxx/fwd_kernel1.cuh:88-103)
 // ---------------------------------------------------------------------------------
+// Also ranks the sequences by decreasing length (order[rank] = sequence; ties by index) when the batch is small
+// enough for the quadratic count: the recurrence starts the longest chains first and keeps them apart.
 __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __restrict__ cu, int64_t N,
-                                                           int32_t* __restrict__ prefix) {
+                                                           int32_t* __restrict__ prefix, int32_t* __restrict__ order) {
     __shared__ int64_t part[1024];
     const int tid = threadIdx.x;
     const int64_t per = (N + 1023) / 1024;
@@ -45,6 +47,17 @@ __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __rest
         run += (len + kChunk - 1) / kChunk;
     }
     if (tid == 1023) prefix[N] = (int32_t)part[1023];
+    if (order != nullptr) {
+        for (int64_t n = tid; n < N; n += 1024) {
+            const int64_t len_n = cu[n + 1] - cu[n];
+            int rank = 0;
+            for (int64_t m = 0; m < N; ++m) {
+                const int64_t len_m = cu[m + 1] - cu[m];
+                rank += (len_m > len_n || (len_m == len_n && m < n)) ? 1 : 0;
+            }
+            order[rank] = (int32_t)n;
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------
@@ -201,8 +214,8 @@ __global__ void __launch_bounds__(128) recurrence_kernel(TwoPassArgs a) {
 // ---------------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------------
-void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, cudaStream_t stream) {
-    tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix);
+void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, cudaStream_t stream) {
+    tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix, seq_order);
 }
 
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
@@ -243,6 +256,7 @@ void fill_args(const fkda_fwd_params& p, TwoPassArgs* out) {
     a.slab_c0 = 0;
     a.slab_chunks = 0;
     a.tile_prefix = reinterpret_cast<int32_t*>(base + kWsHeaderBytes);
+    a.seq_order = (varlen && p.N <= kSeqOrderMaxN) ? a.tile_prefix + (p.N + 1) : nullptr;
     a.workspace = base + kWsHeaderBytes + ws_prefix_bytes(p.N);
 }
 
@@ -255,7 +269,7 @@ int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launche
     const bool do_prep = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_PREPARE);
     const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
     if (varlen && do_prep) {
-        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, stream);
+        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order), stream);
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {
