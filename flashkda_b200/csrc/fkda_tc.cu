@@ -547,7 +547,7 @@ namespace fkda {
 // ---------------------------------------------------------------------------------
 // Segment scheduling is used when there are more chains than a B200 can hold at once (3 per SM);
 // with fewer chains every chain has its own slot and whole chains are the work items.
-constexpr int64_t kSegThresholdChains = 384;
+constexpr int64_t kSegThresholdChains = 148 * kTcChains;  // every chain has its own chain slot up to here
 constexpr int kSegChunksMax = 64, kSegChunksMin = 16;
 // Segment length: 64 chunks when there is plenty of work (the hand-over of a 32 KB state costs about one chunk
 // step), shorter when the whole problem is only a few segments per chain slot, so that 512 chains of 64 chunks

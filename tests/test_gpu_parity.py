@@ -237,13 +237,13 @@ def test_tensor_core_path_matches_cuda_core_path():
 
 
 def test_segment_scheduling_many_chains():
-    """More chains than the GPU holds at once (> 384): the tensor-core path then schedules 64-chunk
-    segments and hands the state from one segment to the next through the workspace.  Long and short
+    """More chains than the GPU holds at once (> 444 = 3 per SM): the tensor-core path then schedules
+    segments of chunks and hands the state from one segment to the next through the workspace.  Long and short
     sequences mixed, so that chains span one to three segments."""
     gen = torch.Generator().manual_seed(5)
     lens = torch.randint(1, 2500, (100,), generator=gen).tolist()
     lens[7], lens[50], lens[99] = 1, 1024, 3000
-    w = Workload("seg", 1, sum(lens), 4, state_in="bf16", state_out="bf16", seq_lens=lens)
+    w = Workload("seg", 1, sum(lens), 5, state_in="bf16", state_out="bf16", seq_lens=lens)
     inp = make_inputs(w, seed=12)
     ref_out, ref_hT = run_oracle(inp)
     out, hT = run_gpu(inp, "tc")
@@ -254,7 +254,7 @@ def test_segment_scheduling_many_chains():
 
 
 def test_segment_scheduling_fixed_batch():
-    w = Workload("segf", 50, 1200, 8, state_in="fp32", state_out="fp32")
+    w = Workload("segf", 60, 1200, 8, state_in="fp32", state_out="fp32")
     inp = make_inputs(w, seed=13)
     out, hT = run_gpu(inp, "tc")
     out2, hT2 = run_gpu(inp, "twopass")
@@ -290,8 +290,8 @@ def test_recurrence_kernel_variants_agree(monkeypatch):
     print(f"tensor-memory state variant vs shared-memory variant: out mismatch {mism:.3e}")
     assert oracle.err_ratio(out_t, out_s) <= 2e-3
     assert oracle.err_ratio(hT_t, hT_s) <= 1e-3
-    # bf16 states and the segment queue (more than 384 chains) through both variants
-    lens2 = torch.randint(1, 1500, (70,), generator=torch.Generator().manual_seed(3)).tolist()
+    # bf16 states and the segment queue (more than 444 chains) through both variants
+    lens2 = torch.randint(1, 1500, (80,), generator=torch.Generator().manual_seed(3)).tolist()
     w2 = Workload("var2", 1, sum(lens2), 6, state_in="bf16", state_out="bf16", seq_lens=lens2)
     inp2 = make_inputs(w2, seed=22)
     out_s2, hT_s2 = run_gpu(inp2, "tc")
