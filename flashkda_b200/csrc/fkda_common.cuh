@@ -124,6 +124,14 @@ __device__ __forceinline__ void mma_f16_f16acc(uint32_t& d0, uint32_t& d1, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
 }
 // bf16 operands, fp32 accumulators
+// Four 8x8 b16 matrices from shared memory into mma.sync fragment registers: lane 8m + r gives the address of
+// row r (16 bytes) of matrix m; thread (g = lane / 4, t = lane % 4) receives elements (g, 2t), (g, 2t + 1) of each.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* row_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
 __device__ __forceinline__ void mma_bf16_f32acc(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1) {
     asm volatile(

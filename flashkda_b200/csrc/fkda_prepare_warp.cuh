@@ -225,27 +225,24 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         float l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
         float m0[4] = {0.f, 0.f, 0.f, 0.f}, m1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
+        // lane 8m + r addresses row r of the m-th 8x8 matrix of a fragment: matrix m of an A fragment is (row group
+        // m & 1, K chunk m >> 1), matrix m of the B pair is (K chunk m & 1, row group m >> 1); rows are 16 bytes
+        const int lr = lane & 7, lm = lane >> 3;
+        const uint8_t* a_row = sm.b1 + (lm >> 1) * kTcB1Lbo + (lm & 1) * 128 + lr * 16;
+        const uint8_t* b_row = sm.kikr + (lm & 1) * kPwKiLbo + (lm >> 1) * 128 + lr * 16;
+#pragma unroll
         for (int j = 0; j < kD / 16; ++j) {
-            // element (row, 16j + 2t [+8]) of a K-major core-matrix tile: chunk 2j [+1], row group, row, 4t bytes
-            const uint8_t* kib = sm.kikr + 2 * j * kPwKiLbo + g * 16 + 4 * t;
-            const uint32_t b00 = *reinterpret_cast<const uint32_t*>(kib);
-            const uint32_t b01 = *reinterpret_cast<const uint32_t*>(kib + kPwKiLbo);
-            const uint32_t b10 = *reinterpret_cast<const uint32_t*>(kib + 128);
-            const uint32_t b11 = *reinterpret_cast<const uint32_t*>(kib + kPwKiLbo + 128);
-            const uint8_t* ab = sm.b1 + 2 * j * kTcB1Lbo + g * 16 + 4 * t;
+            uint32_t b00, b01, b10, b11;
+            ldmatrix_x4(b00, b01, b10, b11, b_row + 2 * j * kPwKiLbo);
             {
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(ab);
-                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(ab + 128);
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(ab + kTcB1Lbo);
-                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(ab + kTcB1Lbo + 128);
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4(a0, a1, a2, a3, a_row + 2 * j * kTcB1Lbo);
                 mma_bf16_f32acc(l0, a0, a1, a2, a3, b00, b01);  // columns 0-7
                 mma_bf16_f32acc(l1, a0, a1, a2, a3, b10, b11);  // columns 8-15
             }
             {
-                const uint32_t a0 = *reinterpret_cast<const uint32_t*>(ab + 256);  // qd = rows 16..31
-                const uint32_t a1 = *reinterpret_cast<const uint32_t*>(ab + 256 + 128);
-                const uint32_t a2 = *reinterpret_cast<const uint32_t*>(ab + 256 + kTcB1Lbo);
-                const uint32_t a3 = *reinterpret_cast<const uint32_t*>(ab + 256 + kTcB1Lbo + 128);
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4(a0, a1, a2, a3, a_row + 2 * j * kTcB1Lbo + 256);  // qd = rows 16..31
                 mma_bf16_f32acc(m0, a0, a1, a2, a3, b00, b01);
                 mma_bf16_f32acc(m1, a0, a1, a2, a3, b10, b11);
             }
