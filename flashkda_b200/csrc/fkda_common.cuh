@@ -185,6 +185,15 @@ __device__ __forceinline__ void store_c_frag_h(__half* Z, int ld, int lane, cons
     *reinterpret_cast<uint32_t*>(Z + g * ld + 2 * t + 8) = c.r[2];
     *reinterpret_cast<uint32_t*>(Z + (g + 8) * ld + 2 * t + 8) = c.r[3];
 }
+// Transposes each 8x8 tile of a fragment in registers: turns the C (= A) fragment of a 16x16 row-major matrix
+// into its B fragment (tile (rows 8i.., cols 8j..) of register i + 2j becomes the pair column of the same register).
+__device__ __forceinline__ Frag16 c_to_b_frag_h(const Frag16& c) {
+    Frag16 b;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(b.r[i]) : "r"(c.r[i]));
+    return b;
+}
 __device__ __forceinline__ Frag16 mma16x16_h(const Frag16& a, const Frag16& b) {
     Frag16 c;
     mma_f16_f16acc(c.r[0], c.r[1], a.r[0], a.r[1], a.r[2], a.r[3], b.r[0], b.r[1], 0u, 0u);
@@ -221,16 +230,13 @@ __device__ __forceinline__ void neumann_inverse_warp(__half* Ls, __half* Ws, int
     // A-fragment and C-fragment register layouts coincide for a 16x16 row-major matrix
     // (regs: [g][2t], [g+8][2t], [g][2t+8], [g+8][2t+8]), so INV can be reused as A directly.
     Frag16 pow_a = load_a_frag_h(Ls, ld, lane);  // L
-    Frag16 pow_b = load_b_frag_h(Ls, ld, lane);
-    __syncwarp();
+    Frag16 pow_b = c_to_b_frag_h(pow_a);         // the powers stay in registers: B fragments by register transposes
+    (void)Ws;
 #pragma unroll
     for (int step = 0; step < 3; ++step) {
         Frag16 p2 = mma16x16_h(pow_a, pow_b);  // L^(2^(step+1))
-        store_c_frag_h(Ws, ld, lane, p2);
-        __syncwarp();
-        pow_b = load_b_frag_h(Ws, ld, lane);
+        pow_b = c_to_b_frag_h(p2);
         pow_a = p2;
-        __syncwarp();
         Frag16 m = mma16x16_h(inv_c, pow_b);  // INV * L^(2^(step+1))
 #pragma unroll
         for (int i = 0; i < 4; ++i) inv_c.r[i] = hadd2_u32(inv_c.r[i], m.r[i]);
