@@ -146,45 +146,11 @@ __device__ __forceinline__ uint32_t hadd2_u32(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t*>(&z);
 }
 
-// 16x16 fp16 product C = A * B by one warp, all three row-major in shared memory with
-// row pitch `ld` halves (ld even).  Fragments are fetched with plain 32/16-bit loads.
-// A-fragment of row-major X: regs {X[g][2t..], X[g+8][2t..], X[g][2t+8..], X[g+8][2t+8..]}.
+// 16x16 fp16 matrices held by one warp as mma.sync fragments.  A / C fragment of a row-major X:
+// regs {X[g][2t..], X[g+8][2t..], X[g][2t+8..], X[g+8][2t+8..]} with g = lane / 4, t = lane % 4.
 struct Frag16 {
     uint32_t r[4];
 };
-__device__ __forceinline__ Frag16 load_a_frag_h(const __half* X, int ld, int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    Frag16 f;
-    f.r[0] = *reinterpret_cast<const uint32_t*>(X + g * ld + 2 * t);
-    f.r[1] = *reinterpret_cast<const uint32_t*>(X + (g + 8) * ld + 2 * t);
-    f.r[2] = *reinterpret_cast<const uint32_t*>(X + g * ld + 2 * t + 8);
-    f.r[3] = *reinterpret_cast<const uint32_t*>(X + (g + 8) * ld + 2 * t + 8);
-    return f;
-}
-// B-fragments (both n-halves) of row-major Y[k][n]: reg pairs {Y[2t][n],Y[2t+1][n]}, {Y[2t+8][n],Y[2t+9][n]}
-// for n = g (regs 0,1) and n = g + 8 (regs 2,3).
-__device__ __forceinline__ Frag16 load_b_frag_h(const __half* Y, int ld, int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    auto pk = [&](int k, int n) {
-        __half2 v = __halves2half2(Y[k * ld + n], Y[(k + 1) * ld + n]);
-        return *reinterpret_cast<uint32_t*>(&v);
-    };
-    Frag16 f;
-    f.r[0] = pk(2 * t, g);
-    f.r[1] = pk(2 * t + 8, g);
-    f.r[2] = pk(2 * t, g + 8);
-    f.r[3] = pk(2 * t + 8, g + 8);
-    return f;
-}
-// C-fragment layout (fp16 accumulators): regs {C[g][2t..], C[g+8][2t..]} for columns 0-7,
-// then the same for columns 8-15.
-__device__ __forceinline__ void store_c_frag_h(__half* Z, int ld, int lane, const Frag16& c) {
-    const int g = lane >> 2, t = lane & 3;
-    *reinterpret_cast<uint32_t*>(Z + g * ld + 2 * t) = c.r[0];
-    *reinterpret_cast<uint32_t*>(Z + (g + 8) * ld + 2 * t) = c.r[1];
-    *reinterpret_cast<uint32_t*>(Z + g * ld + 2 * t + 8) = c.r[2];
-    *reinterpret_cast<uint32_t*>(Z + (g + 8) * ld + 2 * t + 8) = c.r[3];
-}
 // Transposes each 8x8 tile of a fragment in registers: turns the C (= A) fragment of a 16x16 row-major matrix
 // into its B fragment (tile (rows 8i.., cols 8j..) of register i + 2j becomes the pair column of the same register).
 __device__ __forceinline__ Frag16 c_to_b_frag_h(const Frag16& c) {
@@ -205,33 +171,28 @@ __device__ __forceinline__ Frag16 mma16x16_h(const Frag16& a, const Frag16& b) {
 //   (I + L)^-1 = (I - L)(I + L^2)(I + L^4)(I + L^8)
 // with fp16 products/accumulators and fp16 additions, result rounded to bf16
 // (csrc/smxx/utils.cuh:262-311; tests/torch_ref.py:221-229).
-// Ls: L (row-major, pitch ld); Ws: scratch 16 x ld halves; inv_out: bf16 [16][16], dense row-major
-// (kCanonical = false) or in the UMMA canonical K-major layout (tc_sq_off).  Ws is clobbered.
+// L: the matrix as an mma.sync A / C fragment (what the product that forms it leaves in registers); inv_out:
+// bf16 [16][16], dense row-major (kCanonical = false) or in the UMMA canonical K-major layout (tc_sq_off).
 // All 32 lanes of the warp must call.
 template <bool kCanonical>
-__device__ __forceinline__ void neumann_inverse_warp(__half* Ls, __half* Ws, int ld, uint8_t* inv_out, int lane) {
+__device__ __forceinline__ void neumann_inverse_warp(const Frag16& L, uint8_t* inv_out, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    // INV0 = I - L in C-fragment coordinates
+    // INV0 = I - L in C-fragment coordinates (register i: row g + 8 (i & 1), columns 2t + 8 (i >> 1), + 1)
     Frag16 inv_c;
-    {
-        auto el = [&](int r, int c) {
-            __half x = Ls[r * ld + c];
-            return (r == c) ? __hsub(__float2half_rn(1.0f), x) : __hneg(x);
-        };
-        auto pk = [&](int r, int c) {
-            __half2 v = __halves2half2(el(r, c), el(r, c + 1));
-            return *reinterpret_cast<uint32_t*>(&v);
-        };
-        inv_c.r[0] = pk(g, 2 * t);
-        inv_c.r[1] = pk(g + 8, 2 * t);
-        inv_c.r[2] = pk(g, 2 * t + 8);
-        inv_c.r[3] = pk(g + 8, 2 * t + 8);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = g + 8 * (i & 1), c = 2 * t + 8 * (i >> 1);
+        const __half2 x = *reinterpret_cast<const __half2*>(&L.r[i]);
+        const __half one = __float2half_rn(1.0f);
+        const __half e0 = (r == c) ? __hsub(one, __low2half(x)) : __hneg(__low2half(x));
+        const __half e1 = (r == c + 1) ? __hsub(one, __high2half(x)) : __hneg(__high2half(x));
+        const __half2 v = __halves2half2(e0, e1);
+        inv_c.r[i] = *reinterpret_cast<const uint32_t*>(&v);
     }
     // A-fragment and C-fragment register layouts coincide for a 16x16 row-major matrix
-    // (regs: [g][2t], [g+8][2t], [g][2t+8], [g+8][2t+8]), so INV can be reused as A directly.
-    Frag16 pow_a = load_a_frag_h(Ls, ld, lane);  // L
+    // (regs: [g][2t], [g+8][2t], [g][2t+8], [g+8][2t+8]), so L and INV can be used as A directly.
+    Frag16 pow_a = L;
     Frag16 pow_b = c_to_b_frag_h(pow_a);         // the powers stay in registers: B fragments by register transposes
-    (void)Ws;
 #pragma unroll
     for (int step = 0; step < 3; ++step) {
         Frag16 p2 = mma16x16_h(pow_a, pow_b);  // L^(2^(step+1))

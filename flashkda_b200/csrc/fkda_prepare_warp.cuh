@@ -14,7 +14,6 @@
 
 namespace fkda {
 
-constexpr int kPwLd16 = 20;   // fp16 row pitch of the 16x16 matrices
 constexpr int kPwKiLbo = 272;  // ki tile: K-major core matrices, 16-byte K chunks 272 bytes apart (256 + 16 padding)
 
 // Per-warp shared memory.  b1 is the B1 part of the record ([kd; qd] in its final UMMA layout, see
@@ -24,8 +23,6 @@ constexpr int kPwKiLbo = 272;  // ki tile: K-major core matrices, 16-byte K chun
 struct alignas(16) PrepWarpSmem {
     uint8_t b1[kTcB1Bytes];
     uint8_t kikr[kTcKrBytes];
-    __half L[kChunk][kPwLd16];
-    __half W[kChunk][kPwLd16];
     float beta_act[kChunk];
 };
 static_assert(16 * kPwKiLbo <= kTcKrBytes, "the ki tile fits the KR buffer");
@@ -220,6 +217,7 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
 
     // ---- L = fp16(kd ki^T) masked * fp16(beta), Mqk = bf16(qd ki^T) masked: mma.sync m16n8k16
     //      bf16 -> fp32, operand fragments fetched with conflict-free 32-bit loads ----
+    Frag16 lfrag;  // L as the A / C fragment the inverse starts from
     {
         const int g = lane >> 2, t = lane & 3;
         float l0[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -258,7 +256,8 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
                 const __half bh = __float2half_rn(sm.beta_act[i]);
                 const __half h0 = (i > j) ? __hmul(__float2half_rn(x0), bh) : __float2half_rn(0.0f);
                 const __half h1 = (i > j + 1) ? __hmul(__float2half_rn(x1), bh) : __float2half_rn(0.0f);
-                *reinterpret_cast<__half2*>(&sm.L[i][j]) = __halves2half2(h0, h1);
+                const __half2 lh = __halves2half2(h0, h1);
+                lfrag.r[hr + 2 * nt] = *reinterpret_cast<const uint32_t*>(&lh);
                 const uint32_t m = pack_bf2((i >= j) ? y0 : 0.0f, (i >= j + 1) ? y1 : 0.0f);
                 if constexpr (kTc)
                     *reinterpret_cast<uint32_t*>(ws + kTcMqk + tc_sq_off(i, j)) = m;
@@ -296,7 +295,7 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
             sm100::bulk_commit_group();
         }
     }
-    neumann_inverse_warp<kTc>(&sm.L[0][0], &sm.W[0][0], kPwLd16, ws + (kTc ? kTcInv : kWsInv), lane);
+    neumann_inverse_warp<kTc>(lfrag, ws + (kTc ? kTcInv : kWsInv), lane);
     if constexpr (kTc) {  // the tiles are rewritten by the next chunk: the copies must have read them
         if (lane == 0) sm100::bulk_wait_group_read<0>();
     }
