@@ -363,3 +363,15 @@ def test_concurrent_host_threads_share_the_slab_pipeline():
     for i in range(2):
         for out, hT in results[i]:
             assert torch.equal(out, refs[i][0]) and torch.equal(hT, refs[i][1])
+
+
+def test_many_short_sequences_beyond_the_length_ranking_limit(algo):
+    """600 ragged sequences: more than the 512 the prefix kernel ranks by length, so chains start in input order."""
+    gen = torch.Generator().manual_seed(9)
+    lens = torch.randint(0, 40, (600,), generator=gen).tolist()
+    lens[0], lens[299], lens[599] = 1, 0, 37
+    w = Workload("many", 1, sum(lens), 2, state_in="fp32", state_out="fp32", seq_lens=lens, lower_bound=-2.0)
+    inp = make_inputs(w, seed=14)
+    ref_out, ref_hT = run_oracle(inp)
+    out, hT = run_gpu(inp, algo)
+    check_against(out, hT, ref_out, ref_hT)
