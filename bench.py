@@ -4,13 +4,16 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload cfg4] [--algo auto]
 
-N > 1 is launched with torch.distributed.run (one rank per GPU); every rank processes its own
-copy of the per-GPU workload (sequences are independent: no data-path collective, weak
-scaling).  Rank 0 prints ONE JSON line.
+N > 1 is launched with torch.distributed.run (one rank per GPU).  The default is STRONG scaling: the
+workload is one fixed problem whose sequences are partitioned over the ranks (cfg4: B = 8 sequences,
+8 / N per GPU; every sequence is generated from its own seed, so N = 1 and N = 8 process the same
+data); sequences are independent, so there is no data-path collective.  ``--scaling weak`` gives every
+rank its own full copy of the workload instead.  Rank 0 prints ONE JSON line.
 
   value    whole-job tokens/s with inputs resident in HBM (CUDA events, max over ranks)
   e2e      the same through the host-buffer API: pinned host inputs -> H2D -> forward -> D2H
-  roofline dominant kernel: algorithmic bytes / its measured launch time vs measured HBM peak
+  roofline the whole forward (both kernels back to back): algorithmic bytes / step time vs measured HBM
+           peak; per kernel, its OWN bytes (inputs + records it reads and writes) / its launch time
   cpu_baseline  the CPU oracle (a port of the reference's torch_ref numerics) on a bounded sample
 
 --impl reference times the CPU oracle alone (the reference has no CPU implementation of its
@@ -44,15 +47,16 @@ def needs_l2_flush(w):
     return algorithmic_bytes(w) < 4 * L2_BYTES
 
 
-def config_dict(w, algo):
+def config_dict(w, algo, b_per_gpu=None, sharding=None):
     """The workload description both arms print."""
     from flashkda_b200.synth import algorithmic_bytes
-    return {"workload": w.name, "B_per_gpu": w.B, "T": w.T, "H": w.H, "K": 128, "V": 128, "chunk": 16,
+    return {"workload": w.name, "B": w.B, "B_per_gpu": w.B if b_per_gpu is None else b_per_gpu, "T": w.T, "H": w.H,
+            "K": 128, "V": 128, "chunk": 16,
             "lower_bound": w.lower_bound, "state": w.state_out or w.state_in or "none",
             "varlen_sequences": w.n_seqs if w.seq_lens else 0, "algo": algo,
             "l2_policy": ("L2 flushed between timed steps (512 MB write, outside the timed events)" if needs_l2_flush(w)
                           else "inputs exceed L2 (%.1f GB per step)" % (algorithmic_bytes(w) / 1e9)),
-            "sharding": "independent sequences per GPU, no collective"}
+            "sharding": sharding or "independent sequences per GPU, no collective"}
 
 
 def parse():
@@ -63,6 +67,9 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--algo", default=None)
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: strong = the workload's sequences are partitioned over the ranks (default); "
+                         "weak = every rank runs its own full copy")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--seq-parts", type=int, default=1,
@@ -220,12 +227,24 @@ def run_ours(a):
     # One long sequence (cfg5) on several GPUs: context parallel, every rank holds T / N tokens
     # (strong scaling, one all-gather of the per-shard state maps per step).
     cp_mode = w.name == "cfg5" and world > 1
+    strong = cp_mode   # whether the ranks share ONE problem (value = its tokens / time) or each run their own
     if cp_mode:
         from flashkda_b200 import cp
         from flashkda_b200.synth import Workload
         w_local = Workload("cfg5-shard", 1, w.T // world // 16 * 16, w.H, lower_bound=w.lower_bound,
                            state_out=w.state_out)
         inp = make_inputs(w_local, device=dev, seed=rank)
+    elif world > 1 and a.scaling == "strong" and w.seq_lens is None and w.B % world == 0:
+        # one fixed problem: this rank takes B / N of its sequences (contiguous), no collective on the data path
+        from flashkda_b200.synth import Workload, make_inputs_partition
+        per = w.B // world
+        w_local = Workload(w.name, per, w.T, w.H, lower_bound=w.lower_bound, state_in=w.state_in, state_out=w.state_out)
+        inp = make_inputs_partition(w, rank * per, per, device=dev)
+        strong = True
+    elif world == 1 and w.seq_lens is None:
+        from flashkda_b200.synth import make_inputs_partition
+        w_local = w
+        inp = make_inputs_partition(w, 0, w.B, device=dev)   # the same data as the partitioned runs
     else:
         w_local = w
         inp = make_inputs(w, device=dev, seed=rank)
@@ -294,24 +313,21 @@ def run_ours(a):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total = float(t.item())
     ms_step = ms_total / a.steps
-    value = world * w_local.tokens / (ms_step * 1e-3)
+    job_tokens = w.tokens if (strong and not cp_mode) else world * w_local.tokens   # tokens of the whole job per step
+    value = job_tokens / (ms_step * 1e-3)
 
     # ---- each kernel of the forward alone (CUDA events on the launching stream); the slower one is
     #      the dominant kernel the roofline line describes ----
     # (the tensor-core recurrence has a one-chain-per-CTA variant that the launcher picks when there are no more
-    #  (sequence, head) chains than SMs; otherwise the three-chains-per-CTA kernel with the state copy in tensor
-    #  memory runs, or its shared-memory sibling when $FKDA_TC_SS is set)
+    #  (sequence, head) chains than SMs; otherwise the three-chains-per-CTA kernel runs)
     n_seqs = (len(inp["cu_seqlens"]) - 1) if inp.get("cu_seqlens") is not None else w_local.B
-    wide = (n_seqs * w.H <= torch.cuda.get_device_properties(dev).multi_processor_count
-            and not os.environ.get("FKDA_TC_NO_WIDE"))
+    wide = n_seqs * w.H <= torch.cuda.get_device_properties(dev).multi_processor_count
     names = {"twopass": ("fkda::prepare_warp_kernel", "fkda::recurrence_kernel")}.get(
-        algo, ("fkda::prepare_warp_kernel", "fkda::recurrence_tc_wide_kernel" if wide else
-               ("fkda::recurrence_tc_kernel" if os.environ.get("FKDA_TC_SS") else "fkda::recurrence_tc_ts_kernel")))
+        algo, ("fkda::prepare_warp_kernel", "fkda::recurrence_tc_wide_kernel" if wide else "fkda::recurrence_tc_ts_kernel"))
     kernel_times = {}
     n_phase = 3
     barrier()
-    decode = (w_local.T == 1 and inp.get("cu_seqlens") is None and algo != "twopass"
-              and not os.environ.get("FKDA_NO_DECODE"))
+    decode = w_local.T == 1 and inp.get("cu_seqlens") is None and algo != "twopass"
     if decode and not cp_mode and a.seq_parts == 1:
         # one token per sequence: the library runs its single decode kernel (no phases to time apart)
         kernel_name, kernel_ms = "fkda::decode_kernel", ms_step
@@ -339,7 +355,7 @@ def run_ours(a):
     # ---- end to end through the host-buffer API ----
     e2e = None
     if not a.no_e2e and not cp_mode:
-        e2e = measure_e2e(a, w, inp, dev, world, algo, fwd_host)
+        e2e = measure_e2e(a, w_local, inp, dev, world, algo, fwd_host, job_tokens)
 
     if world > 1:
         dist.barrier()
@@ -353,16 +369,36 @@ def run_ours(a):
         peak_gbs, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
     else:
         peak_gbs, peak_src = 6650.0, "fallback"
+    # Roofline.  Headline: the WHOLE forward of this GPU (all its kernels back to back) on the algorithmic bytes
+    # (q, k, v, g, beta read, out written, states in and out).  Beside it every kernel on its OWN bytes: what it must
+    # read and write given the two-kernel split (the prepare kernel reads q, k, g, beta and writes the chunk
+    # records; the recurrence reads the records and v, writes out, and moves the states).
     alg_bytes = algorithmic_bytes(w_local) * (world if cp_mode else 1)
-    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        entry = json.load(open(tpath)).get(kernel_name, {})
+    achieved = alg_bytes / (ms_step * 1e-3) / 1e9
+    th = w_local.tokens * w.H
+    units = ((w_local.tokens + 15) // 16) * w.H
+    state_bytes = alg_bytes - th * 1282 if not cp_mode else 0
+    rec = {"twopass": 13824}.get(algo, 14656)
+    own = {"fkda::prepare_warp_kernel": th * 770 + units * rec,
+           "fkda::decode_kernel": alg_bytes}
+    for n in names[1:]:
+        own[n] = units * rec + th * 512 + state_bytes
+    tdb = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))) \
+        if os.path.exists(os.path.join(ROOT, "profiles", "traffic.json")) else {}
+    per_kernel, traffic = {}, 0.0
+    for name, ms in kernel_times.items():
+        entry = tdb.get(name, {})
+        t_bytes = None
         if entry.get("bytes_per_unit") is not None:  # scaled from the small ncu capture by the (chunk, head) units
-            traffic = entry["bytes_per_unit"] * ((w_local.tokens + 15) // 16) * w.H
+            t_bytes = entry["bytes_per_unit"] * units
         elif entry.get("traffic_over_algorithmic") is not None:  # state-bound kernels: scaled by the algorithmic bytes
-            traffic = entry["traffic_over_algorithmic"] * alg_bytes
+            t_bytes = entry["traffic_over_algorithmic"] * alg_bytes
+        traffic = None if (traffic is None or t_bytes is None) else traffic + t_bytes
+        ob = own.get(name)
+        per_kernel[name] = {"ms": ms, "own_bytes": ob, "achieved": None if ob is None else ob / (ms * 1e-3) / 1e9,
+                            "frac": None if ob is None else ob / (ms * 1e-3) / 1e9 / peak_gbs, "traffic": t_bytes}
+    if not kernel_times:
+        traffic = None
 
     cpu = None
     if not a.no_cpu and world == 1:
@@ -374,15 +410,18 @@ def run_ours(a):
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if cp_mode else "weak", "vs_baseline": None,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": dict(config_dict(w, algo), **({"sharding": "context parallel: T/N tokens per GPU, NCCL all-gather "
-                                                 "of per-shard state maps"} if cp_mode else {})),
-        "tflops": world * algorithmic_flops(w_local) / (ms_step * 1e-3) / 1e12,
-        "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak_gbs, "unit": "GB/s",
-                     "frac": achieved / peak_gbs, "peak_source": peak_src, "traffic": traffic,
-                     "kernel_ms": kernel_ms, "kernels_ms": kernel_times, "algorithmic_bytes_per_launch": alg_bytes,
-                     "whole_forward_frac": alg_bytes / (ms_step * 1e-3) / 1e9 / peak_gbs},
+        "config": config_dict(w, algo, w_local.B,
+                              "context parallel: T/N tokens per GPU, NCCL all-gather of per-shard state maps" if cp_mode
+                              else ("one problem, B/N sequences per GPU (contiguous), no collective" if strong else None)),
+        "tflops": job_tokens * w.H * (algorithmic_flops(w_local) / max(1, w_local.tokens * w.H)) / (ms_step * 1e-3) / 1e12,
+        # per GPU: the forward of this rank's share (all kernels of a step) against the measured copy bandwidth
+        "roofline": {"bound": "hbm", "kernel": "whole forward: " + " + ".join(k.split("::")[-1] for k in kernel_times)
+                     if kernel_times else kernel_name,
+                     "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                     "peak_source": peak_src, "traffic": traffic, "algorithmic_bytes_per_step": alg_bytes,
+                     "slowest_kernel": kernel_name, "kernels": per_kernel},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * a.steps, "clocks": clocks,
     }
     print(json.dumps(line))
@@ -390,7 +429,7 @@ def run_ours(a):
         dist.destroy_process_group()
 
 
-def measure_e2e(a, w, inp, dev, world, algo, fwd_host):
+def measure_e2e(a, w, inp, dev, world, algo, fwd_host, job_tokens):
     """Pinned host buffers -> device -> forward -> host, every step, through fwd_host."""
     import torch
     import torch.distributed as dist
@@ -440,7 +479,7 @@ def measure_e2e(a, w, inp, dev, world, algo, fwd_host):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dt = float(t.item())
     del host
-    return {"value": world * w.tokens / dt, "unit": UNIT, "h2d_bytes_per_step": int(h2d) * world,
+    return {"value": job_tokens / dt, "unit": UNIT, "h2d_bytes_per_step": int(h2d) * world,
             "d2h_bytes_per_step": int(d2h) * world, "ms_per_step": dt * 1e3, "steps": steps,
             "api": "flashkda_b200.host.fwd_host (pinned host tensors, per-sequence slabs, copy/compute overlap)"}
 

@@ -35,7 +35,7 @@ def _check(cond, msg):
 
 
 def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None, final_state=None,
-        cu_seqlens=None, *, algo: str = None, workspace: torch.Tensor = None, phase_mask: int = 0):
+        cu_seqlens=None, *, algo: str = None, workspace: torch.Tensor = None, phase_mask: int = 0, flags: int = 0):
     """FlashKDA forward; writes ``out`` (and ``final_state``) in place and returns ``None``.
 
     q, k, v, g, out: bf16 ``[B, T, H, 128]``; beta: bf16 ``[B, T, H]`` logits; A_log: fp32
@@ -46,7 +46,12 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
     ``algo`` and ``workspace`` are additions to the reference signature: the implementation
     selector (default from ``$FLASHKDA_B200_ALGO`` or "auto") and an optional caller-owned
     uint8 scratch tensor of at least ``get_workspace_size(...)`` bytes.  ``phase_mask`` is a
-    measurement aid (see ``fkda_fwd_params.phase_mask``); leave it 0.
+    measurement aid (see ``fkda_fwd_params.phase_mask``) and ``flags`` selects kernel variants for tests
+    (``fkda_fwd_params.flags``); leave both 0.
+
+    The call returns without synchronising, so it cannot tell whether a kernel gave up on one of its
+    bounded internal waits (possible only when other long-running kernels hold the GPU's SMs for
+    seconds); ``device_status(workspace)`` reports that after the stream has been synchronised.
     """
     bf16 = torch.bfloat16
     big = (q, k, v, g, beta, out)
@@ -106,21 +111,22 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
     T_total = B * T
     if T_total == 0 and final_state is None:
         return None
-    need = int(L.fkda_workspace_bytes(T_total, H, N, algo_id))
-    if workspace is None:
-        workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
-    else:
-        _check(workspace.is_cuda and workspace.is_contiguous() and workspace.dtype == torch.uint8
-               and workspace.numel() >= need, "workspace must be a contiguous CUDA uint8 tensor of sufficient size")
-
     ptr = lambda t: None if t is None else t.data_ptr()
     p = _lib.FwdParams(
         q=ptr(q), k=ptr(k), v=ptr(v), g=ptr(g), beta=ptr(beta), out=ptr(out), A_log=ptr(A_log), dt_bias=ptr(dt_bias),
         initial_state=ptr(initial_state), final_state=ptr(final_state),
         state_dtype=_lib.FKDA_STATE_FP32 if state_fp32 else _lib.FKDA_STATE_BF16, algo=algo_id,
         cu_seqlens=ptr(cu_seqlens), B=B, T=T, H=H, N=N, token_stride=H * D, beta_token_stride=H,
-        scale=float(scale), lower_bound=lower_bound, workspace=workspace.data_ptr(), workspace_bytes=workspace.numel(),
-        phase_mask=int(phase_mask))
+        scale=float(scale), lower_bound=lower_bound, workspace=None, workspace_bytes=0,
+        phase_mask=int(phase_mask), flags=int(flags))
+    with torch.cuda.device(dev):
+        need = int(L.fkda_workspace_bytes_for(p))  # what this call's path needs (a decode step: 256 bytes)
+    if workspace is None:
+        workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    else:
+        _check(workspace.is_cuda and workspace.is_contiguous() and workspace.dtype == torch.uint8
+               and workspace.numel() >= need, "workspace must be a contiguous CUDA uint8 tensor of sufficient size")
+    p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel()
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         rc = L.fkda_fwd(p, stream)

@@ -8,6 +8,16 @@ LIB_PATH = os.path.join(HERE, "libflashkda_b200.so")
 FKDA_STATE_BF16, FKDA_STATE_FP32 = 0, 1
 ALGO_AUTO, ALGO_TWOPASS, ALGO_TC = 0, 1, 2
 PHASE_PREPARE, PHASE_RECURRENCE = 1, 2
+# fkda_fwd_params.flags (tests and tuning; 0 in production)
+FLAG_NO_DECODE, FLAG_NO_WIDE, FLAG_NO_SLABS, FLAG_NO_SHORT, FLAG_TEST_DROP_PUSH = 1, 2, 4, 8, 16
+
+
+def flags_seg_chunks(n: int) -> int:
+    return (int(n) & 0xff) << 8
+
+
+def flags_wait_ms(ms: int) -> int:
+    return (int(ms) & 0x3fff) << 16
 ALGOS = {"auto": ALGO_AUTO, "twopass": ALGO_TWOPASS, "tc": ALGO_TC}
 
 
@@ -21,7 +31,7 @@ class FwdParams(ctypes.Structure):
         ("token_stride", ctypes.c_int64), ("beta_token_stride", ctypes.c_int64),
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_double),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
-        ("phase_mask", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("phase_mask", ctypes.c_int32), ("flags", ctypes.c_int32),
     ]
 
 
@@ -41,6 +51,8 @@ def lib():
         L.fkda_fwd.argtypes = [ctypes.POINTER(FwdParams), ctypes.c_void_p]
         L.fkda_workspace_bytes.restype = ctypes.c_size_t
         L.fkda_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]
+        L.fkda_workspace_bytes_for.restype = ctypes.c_size_t
+        L.fkda_workspace_bytes_for.argtypes = [ctypes.POINTER(FwdParams)]
         L.fkda_version.restype = ctypes.c_int
         L.fkda_status_string.restype = ctypes.c_char_p
         L.fkda_status_string.argtypes = [ctypes.c_int]

@@ -1,7 +1,5 @@
 // C ABI of the library: argument validation and dispatch to the device implementations.
 // Replaces the reference's host binding (csrc/flash_kda.cpp:28-217) below its tensor checks.
-#include <stdlib.h>
-
 #include "fkda_internal.h"
 
 namespace {
@@ -46,9 +44,21 @@ size_t fkda_workspace_bytes(int64_t T_total, int64_t H, int64_t N, int32_t algo)
     }
 }
 
+// Scratch bytes this particular call needs: never more than fkda_workspace_bytes() for the same totals, and much
+// less where the call takes a path that keeps no per-chunk records (a decode step needs the status word only).
+size_t fkda_workspace_bytes_for(const fkda_fwd_params* p) {
+    if (p == nullptr || p->B <= 0 || p->T < 0 || p->H <= 0 || p->N <= 0) return 0;
+    switch (resolve_algo(p->algo)) {
+        case FKDA_ALGO_TWOPASS: return fkda::twopass_workspace_bytes(p->B * p->T, p->H, p->N);
+        case FKDA_ALGO_TC: return fkda::tc_workspace_bytes_for(*p);
+        default: return 0;
+    }
+}
+
 int fkda_last_launch_count(void) { return g_last_launches; }
 
 int fkda_device_status(const void* workspace, void* stream_v) {
+    if (workspace == nullptr) workspace = fkda::noalloc_scratch_or_null();  // the built-in scratch of fkda_fwd_noalloc
     if (workspace == nullptr) return FKDA_ERR_NULL_POINTER;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     int32_t hdr[2] = {0, 0};
@@ -75,14 +85,14 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
         return FKDA_ERR_ALIGNMENT;
     const int algo = resolve_algo(p->algo);
     if (algo != FKDA_ALGO_TWOPASS && algo != FKDA_ALGO_TC) return FKDA_ERR_BAD_ALGO;
-    const size_t need = fkda_workspace_bytes(T_total, p->H, p->N, algo);
+    const size_t need = fkda_workspace_bytes_for(p);
     if (need > 0 && (p->workspace == nullptr || p->workspace_bytes < need ||
                      (reinterpret_cast<uintptr_t>(p->workspace) & 255u) != 0))
         return FKDA_ERR_WORKSPACE;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     int launches = 0;
     int rc;
-    if (algo == FKDA_ALGO_TC && fkda::decode_eligible(*p) && getenv("FKDA_NO_DECODE") == nullptr)
+    if (algo == FKDA_ALGO_TC && fkda::decode_eligible(*p) && !(p->flags & FKDA_FLAG_NO_DECODE))
         rc = fkda::launch_decode(*p, stream, &launches);  // one token per sequence: state read-modify-write
     else if (algo == FKDA_ALGO_TC)
         rc = fkda::launch_tc(*p, stream, &launches);

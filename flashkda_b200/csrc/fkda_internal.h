@@ -21,9 +21,10 @@ struct TwoPassArgs {
     int32_t* tile_prefix;  // [N + 1] chunk-count prefix (varlen only)
     const int32_t* seq_order;  // [N] sequences by decreasing length (varlen with N <= kSeqOrderMaxN, else nullptr)
     uint8_t* workspace;    // [H][total_tiles] per-chunk records
-    int32_t* queue;        // header word 0: ticket counter of the persistent recurrence (zeroed per call)
+    int32_t* queue;        // header word 0: tail / queue ticket counter of the persistent recurrence (zeroed per call)
     int32_t* status;       // header word 1: device status, 0 ok, else the code of a bounded wait that gave up
-                           // (header words 2, 3: push counter and finished-chain counter of the segment queue)
+                           // (header words 2, 3: push counter and finished-chain counter of the segment queue;
+                           //  words 4..6: claim counters of the three layers of first segments)
     int32_t* qslots;       // segment queue: slot i receives the i-th pushed item (-1 = not yet pushed)
     uint32_t* seg_state;   // [chain][16][128] uint4: bf16 state handed from one segment of a chain to the next
     int32_t seg_chunks;    // chunks per scheduling segment (0 = whole chains)
@@ -33,11 +34,13 @@ struct TwoPassArgs {
     int64_t T, H, N, total_tiles;
     int64_t token_stride, beta_token_stride;
     float scale, gate_scale;
+    uint64_t wait_ns;      // limit of every bounded device-side wait (mbarrier, queue slot)
     bool state_fp32;
+    bool test_drop_push;   // test hook (FKDA_FLAG_TEST_DROP_PUSH): finished segments do not queue their follow-up
 };
 
 // Workspace layout of both two-pass implementations:
-//   [0, 256)  header: int32 ticket counter, device status, push counter, finished-chain counter
+//   [0, 256)  header: int32 ticket counter, device status, push counter, finished-chain counter, 3 layer counters
 //   [256, ..) tile prefix (N + 1 int32, padded to 256 B)
 //   then      H * total_tiles records
 constexpr size_t kWsHeaderBytes = 256;
@@ -48,7 +51,12 @@ inline int64_t ws_tiles_upper_bound(int64_t T_total, int64_t N) { return (T_tota
 
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
 int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
-size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N);
+size_t tc_workspace_bytes(int64_t T_total, int64_t H, int64_t N);   // upper bound for these totals
+size_t tc_workspace_bytes_for(const fkda_fwd_params& p);            // what this particular call needs
+int device_sm_count();
+// Device address of the built-in scratch of fkda_fwd_noalloc on the current device, or nullptr before that
+// entry point's first call there.
+void* noalloc_scratch_or_null();
 int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
 // Decode step (fixed batch, T == 1): one read-modify-write kernel over the states, no workspace records.
 bool decode_eligible(const fkda_fwd_params& p);

@@ -13,6 +13,8 @@
 // race on it, so callers must serialise their use of this entry point per device.  The array keeps
 // the previous call's contents; the only part that has to start from zero (the work-queue counter
 // and the device status word in its header) is cleared by every call before the kernels run.
+#include <atomic>
+
 #include "fkda_internal.h"
 
 namespace {
@@ -23,23 +25,33 @@ namespace {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[FKDA_NOALLOC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {nullptr};
+std::atomic<void*> g_scratch_addr[kMaxDevices];   // zero-initialised; every thread that resolves an address stores the same value
 
 // One-time set-up for the current device: resolves the device address of the array.
-// Runs on the first call per device; that call should happen outside any stream capture.
+// Runs on the first call per device; that call should happen outside any stream capture.  (A first call that
+// takes the slab pipeline -- a fixed batch of few long sequences -- also creates that pipeline's side stream and
+// events, once per device: driver objects, no device memory.)
 int scratch_for_current_device(void** out) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FKDA_ERR_LAUNCH;
-    if (g_scratch_addr[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return FKDA_ERR_LAUNCH;
-        g_scratch_addr[dev] = ptr;
+        g_scratch_addr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = ptr;
     return FKDA_OK;
 }
 
 }  // namespace
+
+namespace fkda {
+void* noalloc_scratch_or_null() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    return g_scratch_addr[dev].load(std::memory_order_acquire);
+}
+}  // namespace fkda
 
 extern "C" {
 
@@ -48,7 +60,7 @@ size_t fkda_noalloc_scratch_bytes(void) { return (size_t)FKDA_NOALLOC_SCRATCH_BY
 int fkda_fwd_noalloc(const fkda_fwd_params* p, void* stream_v) {
     if (p == nullptr) return FKDA_ERR_NULL_POINTER;
     if (p->B <= 0 || p->T < 0 || p->H <= 0 || p->N <= 0) return FKDA_ERR_BAD_SHAPE;
-    const size_t need = fkda_workspace_bytes(p->B * p->T, p->H, p->N, p->algo);
+    const size_t need = fkda_workspace_bytes_for(p);  // by the path this call takes: a decode step needs 256 bytes
     if (need > (size_t)FKDA_NOALLOC_SCRATCH_BYTES) return FKDA_ERR_NOALLOC_TOO_LARGE;
     void* scratch = nullptr;
     int rc = scratch_for_current_device(&scratch);

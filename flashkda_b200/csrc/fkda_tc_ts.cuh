@@ -24,7 +24,7 @@ namespace fkda {
 
 // byte offsets inside one chain's shared-memory block (no state tile)
 constexpr int kTsStage = 0;                                   // kTcStages chunk records
-constexpr int kTsV = kTsStage + kTcStages * kSmStageBytes;    // kTcStages value tiles [16][128] bf16
+constexpr int kTsV = kTsStage + kTcStages * kTcStageBytes;    // kTcStages value tiles [16][128] bf16
 constexpr int kTsOut = kTsV + kTcStages * 4096;               // out tile [16][128] bf16
 constexpr int kTsChainBytes = kTsOut + 4096;
 static_assert(kTsV % 128 == 0 && kTsChainBytes % 128 == 0, "TMA tiles are 128-byte aligned");
@@ -78,12 +78,12 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
     uint32_t full_phase[kTcStages] = {0, 0};
     uint32_t mma_phase = 0;
     bool failed = false;
-    bool first_ticket = true;
+    bool first_claim = true;
 
     while (!failed) {
         // ---- next work item (a segment of a chain) ----
-        if (v == 0) ctl.next_chain[wg] = tc_next_item(a, first_ticket, wg, n_chains, abort_flag);
-        first_ticket = false;
+        if (v == 0) ctl.next_chain[wg] = tc_next_item(a, first_claim, wg, n_chains, abort_flag);
+        first_claim = false;
         named_barrier_sync(bar_id, 128);
         const int item = ctl.next_chain[wg];
         if (item == -3) { failed = true; break; }
@@ -102,7 +102,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
         auto issue_load = [&](int t) {  // one thread: the record of chunk t into stage t % kTcStages
             const int s = t % kTcStages;
             mbar_arrive_expect_tx(&ctl.full[wg][s], (uint32_t)(kTcRecord + kChunk * kD * 2));
-            bulk_g2s(cs + kTsStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[wg][s]);
+            bulk_g2s(cs + kTsStage + s * kTcStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[wg][s]);
             // rows past the end of the tensor arrive as zeros; rows of the next sequence are never used
             tma_load_3d(cs + kTsV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[wg][s]);
         };
@@ -155,11 +155,11 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
 
         for (int t = c0; t < c1; ++t) {
             const int s = t % kTcStages;
-            uint8_t* st = cs + kTsStage + s * kSmStageBytes;
+            uint8_t* st = cs + kTsStage + s * kTcStageBytes;
             const uint32_t st_addr = smem_u32(st);
 
             // ---- operands of chunk t have landed ----
-            if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, a.wait_ns)) { failed = true; break; }
             full_phase[s] ^= 1u;
 
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T, A = the state copy in tensor memory (8 columns per K step) ----
@@ -180,7 +180,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             tc_load_v_column(cs + kTsV + s * 4096, v, len, v_cur);
             uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta)
             tc_load_beta(st, bpk);
-            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, a.wait_ns)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
 
@@ -211,7 +211,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, a.wait_ns)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
             {   // U = bf(D2) replaces u' as the A operand
@@ -240,7 +240,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma[wg], mma_phase, abort_flag, a.wait_ns)) { failed = true; break; }
             mma_phase ^= 1u;
             tc_fence_after_sync();
 

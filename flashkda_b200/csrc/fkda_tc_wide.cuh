@@ -107,7 +107,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
         auto issue_load = [&](int t) {
             const int s = t % kTcStages;
             mbar_arrive_expect_tx(&ctl.full[s], (uint32_t)(kTcRecord + kChunk * kD * 2));
-            bulk_g2s(cs + kTsStage + s * kSmStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[s]);
+            bulk_g2s(cs + kTsStage + s * kTcStageBytes, rec_base + (int64_t)t * kTcRecord, kTcRecord, &ctl.full[s]);
             tma_load_3d(cs + kTsV + s * 4096, &maps.v, 0, h, (int)(bos + (int64_t)t * kChunk), &ctl.full[s]);
         };
         if (threadIdx.x == 0) {
@@ -155,13 +155,13 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
 
         for (int t = c0; t < c1; ++t) {
             const int s = t % kTcStages;
-            uint8_t* st = cs + kTsStage + s * kSmStageBytes;
+            uint8_t* st = cs + kTsStage + s * kTcStageBytes;
             const uint32_t st_addr = smem_u32(st);
             const int len = (int)min((int64_t)kChunk, seq_len - (int64_t)t * kChunk);
             __nv_bfloat16* out_tile = reinterpret_cast<__nv_bfloat16*>(cs + kWideOut + (t & 1) * 4096);
 
             // ---- operands of chunk t have landed (every warpgroup observes it: the helpers read E_tot) ----
-            if (!mbar_wait_bounded(&ctl.full[s], full_phase[s], abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.full[s], full_phase[s], abort_flag, a.wait_ns)) { failed = true; break; }
             full_phase[s] ^= 1u;
             if (wg == 0) {
                 // ---- MMA1: D1[V,32] = S . [kd; qd]^T ----
@@ -180,7 +180,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 tc_load_v_column(cs + kTsV + s * 4096, v, len, v_cur);
                 uint32_t bpk[8];  // bf16x2 pairs of sigmoid(beta)
                 tc_load_beta(st, bpk);
-                if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+                if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, a.wait_ns)) { failed = true; break; }
                 mma_phase ^= 1u;
                 tc_fence_after_sync();
                 // ---- u' = (v (-) bf(u0)) (*) bf(beta) -> A operand (thread = V row) ----
@@ -209,7 +209,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                     }
                     __syncwarp();
                 }
-                if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+                if (!mbar_wait_bounded(&ctl.mma, mma_phase, abort_flag, a.wait_ns)) { failed = true; break; }
                 mma_phase ^= 1u;
                 tc_fence_after_sync();
                 {   // U = bf(D2) replaces u' as the A operand
@@ -236,7 +236,7 @@ recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_co
                 }
             }
             // ---- every warpgroup: the chunk's last MMAs are done ----
-            if (!mbar_wait_bounded(&ctl.mma3, mma3_phase, abort_flag, kTcWaitNs)) { failed = true; break; }
+            if (!mbar_wait_bounded(&ctl.mma3, mma3_phase, abort_flag, a.wait_ns)) { failed = true; break; }
             mma3_phase ^= 1u;
             tc_fence_after_sync();
             const float4* et4 = reinterpret_cast<const float4*>(st + kTcEt);  // gate decay of the 128 state columns

@@ -244,6 +244,9 @@ void fill_args(const fkda_fwd_params& p, TwoPassArgs* out) {
     a.beta_token_stride = p.beta_token_stride;
     a.scale = p.scale;
     a.gate_scale = (float)(p.lower_bound * 1.4426950408889634);  // log2-domain gate (csrc/flash_kda.cpp:128)
+    const uint64_t wait_ms = (uint64_t)((p.flags >> 16) & 0x3fff);
+    a.wait_ns = (wait_ms ? wait_ms : 2000u) * 1000000ull;
+    a.test_drop_push = (p.flags & FKDA_FLAG_TEST_DROP_PUSH) != 0;
     const int64_t T_total = p.B * p.T;
     const bool varlen = p.cu_seqlens != nullptr;
     a.total_tiles = varlen ? ws_tiles_upper_bound(T_total, p.N) : p.N * ((p.T + kChunk - 1) / kChunk);

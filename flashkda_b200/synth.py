@@ -130,6 +130,21 @@ def make_inputs(w: Workload, device="cpu", seed: Optional[int] = None):
                 dt_bias=dt_bias, lower_bound=w.lower_bound, initial_state=h0, final_state=hT, cu_seqlens=cu)
 
 
+def make_inputs_partition(w: Workload, first: int, count: int, device="cpu"):
+    """Sequences ``first .. first + count - 1`` of the fixed batch ``w`` (one rank's share when the batch is
+    partitioned over GPUs).  Every sequence comes from its own seed (``w.seed + 1 + index``) and the per-head
+    parameters from ``w.seed``, so any partition of the batch yields the same data."""
+    assert w.seq_lens is None and 0 <= first and first + count <= w.B
+    one = Workload(w.name, 1, w.T, w.H, lower_bound=w.lower_bound, state_in=w.state_in, state_out=w.state_out)
+    parts = [make_inputs(one, device=device, seed=w.seed + 1 + first + i) for i in range(count)]
+    head = make_inputs(Workload(w.name, 1, 16, w.H), device=device, seed=w.seed)
+    cat = lambda key: None if parts[0][key] is None else torch.cat([p.pop(key) for p in parts], dim=0)
+    out = {key: cat(key) for key in ("q", "k", "v", "g", "beta", "out", "initial_state", "final_state")}
+    out.update(scale=head["scale"], A_log=head["A_log"], dt_bias=head["dt_bias"], lower_bound=w.lower_bound,
+               cu_seqlens=None)
+    return out
+
+
 def make_reference_test_inputs(w: Workload, device="cpu", seed: int = 42):
     """Inputs in the style of the reference's unit tests (tests/test_fwd_full.py:26-44):
     L2-normalised q/k, randn v/g/beta, U[0,1) A_log and dt_bias, arange-valued state."""

@@ -84,19 +84,40 @@ typedef struct fkda_fwd_params {
     int32_t phase_mask;        /* measurement aid for multi-kernel algos: 0 = whole forward; otherwise a
                                   bit set of FKDA_PHASE_* to launch (the workspace must then already hold
                                   what the skipped phases produce) */
-    int32_t reserved;
+    int32_t flags;             /* 0 for normal use; FKDA_FLAG_* bits select kernel variants for tests and tuning */
 } fkda_fwd_params;
+
+/* fkda_fwd_params.flags.  All zero is the production setting. */
+enum {
+    FKDA_FLAG_NO_DECODE = 1,       /* run a T == 1 batch through the chunked kernels instead of the decode kernel */
+    FKDA_FLAG_NO_WIDE = 2,         /* never pick the one-chain-per-CTA recurrence */
+    FKDA_FLAG_NO_SLABS = 4,        /* no slab pipeline (prepare of the next slab beside the recurrence) */
+    FKDA_FLAG_NO_SHORT = 8,        /* run sequences of at most 16 tokens through the general kernels */
+    FKDA_FLAG_TEST_DROP_PUSH = 16  /* TEST ONLY: finished segments do not queue their follow-up, so that the
+                                      work queue starves and its bounded waits give up */
+};
+/* bits 8..15: segment length of the work queue in chunks (0 = automatic; tuning aid)
+ * bits 16..29: limit of every bounded device-side wait in milliseconds (0 = the default of 2000) */
+#define FKDA_FLAGS_SEG_CHUNKS(x) (((x) & 0xff) << 8)
+#define FKDA_FLAGS_WAIT_MS(x) (((x) & 0x3fff) << 16)
 
 /* Scratch bytes one call needs (0 is a valid answer).  Replaces get_workspace_size
  * (csrc/flash_kda.cpp:5-26): same arguments plus the implementation selector. */
 size_t fkda_workspace_bytes(int64_t T_total, int64_t H, int64_t N, int32_t algo);
+
+/* Scratch bytes THIS call needs (<= fkda_workspace_bytes for the same totals): a decode step (fixed batch,
+ * T == 1) needs only the 256-byte header, other calls their records and queue.  No counterpart in the reference. */
+size_t fkda_workspace_bytes_for(const fkda_fwd_params* p);
 
 /* Enqueues the forward pass on `stream` (a cudaStream_t passed as void*). */
 int fkda_fwd(const fkda_fwd_params* p, void* stream);
 
 /* Synchronises `stream`, then reads the device status word that the kernels of the last call
  * using `workspace` left there: FKDA_OK, or FKDA_ERR_DEVICE_STATUS when a kernel gave up on one of
- * its bounded internal waits (its outputs are then invalid).  Other failures: FKDA_ERR_LAUNCH. */
+ * its bounded internal waits (its outputs are then invalid).  Other failures: FKDA_ERR_LAUNCH.
+ * workspace == NULL reads the built-in scratch of fkda_fwd_noalloc on the current device.
+ * fkda_fwd itself never synchronises, so it cannot report this condition: a caller that shares the GPU
+ * with other long-running kernels should poll this after synchronising. */
 int fkda_device_status(const void* workspace, void* stream);
 
 /*
@@ -110,12 +131,17 @@ int fkda_device_status(const void* workspace, void* stream);
  * ignored); the per-chunk scratch comes from a fixed array of FKDA_NOALLOC_SCRATCH_BYTES bytes that
  * every GPU loading this library holds until the process exits.
  *
- * Limit: fkda_workspace_bytes(B*T, H, N, algo) must not exceed FKDA_NOALLOC_SCRATCH_BYTES
- * (roughly H * (B*T/16 + N) <= 2400 chunk records); larger problems return
- * FKDA_ERR_NOALLOC_TOO_LARGE and launch nothing.
- * The call itself performs no cudaMalloc/cudaFree and calls no allocating library routine.
- * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
- * that first call outside of any stream capture.
+ * Limit: fkda_workspace_bytes_for(p) must not exceed FKDA_NOALLOC_SCRATCH_BYTES.  With the default
+ * algorithm a chunk record takes 14 656 bytes and a (sequence, head) chain 32 KB of hand-over state when
+ * the call may be pipelined or queued, so about H * (B*T/16) <= 2 250 chunk records minus 2.2 records per
+ * chain (algo = twopass: 13 824-byte records, about 2 400); a decode step (T == 1) needs 256 bytes whatever
+ * its batch size.  Larger problems return FKDA_ERR_NOALLOC_TOO_LARGE and launch nothing.
+ * The call itself performs no cudaMalloc/cudaFree and allocates no device memory through any library.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); the first
+ * call on a device that takes the slab pipeline (fixed batch, few long sequences) also creates a side
+ * stream and five events, driver objects that hold no device memory.  Make those first calls outside of
+ * any stream capture.
+ * fkda_device_status(NULL, stream) reports whether a bounded wait gave up in the last such call.
  * All calls on a device share the one array: calls whose kernels may overlap on the GPU race with
  * each other, so serialise them (one stream, or explicit ordering).  The array is not cleared
  * between calls; the header words that must start at zero are reset by each call.

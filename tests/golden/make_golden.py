@@ -1,9 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own torch_ref.
 
-Run once, in a container that has the reference checkout (default path
-``/root/reference``; pass another as argv[1]):
+Run once, in a container that has the reference checkout, whose path is the one argument:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 No reference source is copied: the text of ``tests/torch_ref.py`` is read from the
 checkout and executed from its "Numeric helpers" section on (the part before that
@@ -85,7 +84,9 @@ CASES = {
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference/checkout")
+    ref_root = sys.argv[1]
     torch_ref = load_torch_ref(ref_root)
     torch.set_num_threads(os.cpu_count())
     for name, (w, style, store_inputs) in CASES.items():

@@ -10,6 +10,7 @@ import torch
 
 import flashkda_b200
 import oracle
+from flashkda_b200 import _lib
 from flashkda_b200.synth import Workload, make_inputs
 from kda_testlib import run_oracle
 from test_gpu_parity import check_against, run_gpu
@@ -33,13 +34,12 @@ def test_decode_step_matches_oracle(B, H, state_dtype, io):
     check_against(out, hT, ref_out, ref_hT)
 
 
-def test_decode_kernel_matches_general_path(monkeypatch):
+def test_decode_kernel_matches_general_path():
     w = Workload("decg", 96, 1, 16, state_in="fp32", state_out="fp32", lower_bound=-1.0)
     inp = make_inputs(w, seed=7)
     out_d, hT_d = run_gpu(inp, "tc")
     assert flashkda_b200.last_launch_count() == 1
-    monkeypatch.setenv("FKDA_NO_DECODE", "1")
-    out_g, hT_g = run_gpu(inp, "tc")
+    out_g, hT_g = run_gpu(inp, "tc", flags=_lib.FLAG_NO_DECODE | _lib.FLAG_NO_SHORT)
     assert flashkda_b200.last_launch_count() == 2  # prepare + recurrence
     out_c, hT_c = run_gpu(inp, "twopass")
     mism = (out_d != out_g).float().mean().item()

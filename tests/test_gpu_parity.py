@@ -2,25 +2,30 @@
 committed golden fixtures.
 
 Tolerances.  The target states: out within max-abs 2e-2, final_state within 1e-3 relative
-(RMSE ratio, reference tests/test_fwd.py:13-16) against the reference's GPU results.  The CPU
-oracle and the fixtures use exact tanh/exp2 where the GPU uses tanh.approx / ex2.approx, which
-moves results by a few 1e-3 relative; the bounds against them are therefore out max-abs 2e-2,
-out ratio 1e-2 and state ratio 1e-2.  Bit-exact equalities are asserted wherever both sides ran
-on the GPU (chaining, batching, varlen-vs-fixed, implementation-vs-implementation).
+(RMSE ratio, reference tests/test_fwd.py:13-16) against the reference's GPU results; that bar -- in fact
+bit equality -- is asserted in test_reference_gpu_parity.py against outputs of the reference's torch_ref
+produced on a GPU.  The CPU oracle and the CPU-made fixtures used HERE evaluate tanh and exp2 exactly where
+the GPU uses tanh.approx / ex2.approx; measured against the reference's GPU results that modelling gap is up
+to 1.3e-3 on out and 5.3e-4 on the state for ordinary inputs (up to 9e-3 on the state when the gates
+saturate).  The bounds against the CPU oracle are therefore: out max-abs 2e-2, out ratio 4e-3, state ratio
+2e-3; 1e-2 for the saturated-gate sweep.  Bit-exact equalities are asserted wherever both sides ran on the GPU
+(chaining, batching, varlen-vs-fixed, kernel-vs-kernel).
 """
 import pytest
 import torch
 
 import flashkda_b200
 import oracle
+from flashkda_b200 import _lib
 from flashkda_b200.synth import Workload, config, make_inputs, make_reference_test_inputs, to_device
 from kda_testlib import GOLDEN_CASES, load_golden, run_oracle
 
 pytestmark = pytest.mark.gpu
 
 OUT_MAX_ABS = 2e-2
-OUT_RATIO = 1e-2
-STATE_RATIO = 1e-2
+OUT_RATIO = 4e-3
+STATE_RATIO = 2e-3
+SATURATED_RATIO = 1e-2   # constant gates of +-8: tanh.approx vs exact tanh at saturation
 
 
 ALGOS = ["twopass", "tc"]
@@ -31,7 +36,7 @@ def algo(request):
     return request.param
 
 
-def run_gpu(inp, algo=None):
+def run_gpu(inp, algo=None, flags=0):
     d = to_device(inp, "cuda")
     w = d["q"]
     n = d["cu_seqlens"].numel() - 1 if d["cu_seqlens"] is not None else w.shape[0]
@@ -39,22 +44,22 @@ def run_gpu(inp, algo=None):
                      dtype=torch.uint8, device="cuda")
     flashkda_b200.fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["out"], A_log=d["A_log"],
                       dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], initial_state=d["initial_state"],
-                      final_state=d["final_state"], cu_seqlens=d["cu_seqlens"], algo=algo, workspace=ws)
+                      final_state=d["final_state"], cu_seqlens=d["cu_seqlens"], algo=algo, workspace=ws, flags=flags)
     assert flashkda_b200.device_status(ws) == 0, "a kernel gave up on a bounded wait"
     torch.cuda.synchronize()
     assert flashkda_b200.last_launch_count() > 0
     return d["out"].cpu(), None if d["final_state"] is None else d["final_state"].cpu()
 
 
-def check_against(out, hT, ref_out, ref_hT):
+def check_against(out, hT, ref_out, ref_hT, out_ratio=OUT_RATIO, state_ratio=STATE_RATIO):
     assert torch.isfinite(out.float()).all()
     # absolute bound for O(1) outputs; fixtures with the reference's arange-valued initial state reach
     # |out| ~ 1e3, where the bound scales with the magnitude
     assert oracle.max_abs(ref_out, out) <= OUT_MAX_ABS * max(1.0, ref_out.float().abs().max().item())
-    assert oracle.err_ratio(ref_out, out) <= OUT_RATIO
+    assert oracle.err_ratio(ref_out, out) <= out_ratio
     if ref_hT is not None:
         assert hT is not None and torch.isfinite(hT.float()).all()
-        assert oracle.err_ratio(ref_hT.float(), hT.float()) <= STATE_RATIO
+        assert oracle.err_ratio(ref_hT.float(), hT.float()) <= state_ratio
         # every exported state value is bf16-representable (reference: csrc/smxx/utils.cuh:377-378)
         assert torch.equal(hT.to(torch.bfloat16).to(hT.dtype), hT)
 
@@ -130,7 +135,7 @@ def test_gate_stress_cases(algo):
         inp["dt_bias"] = torch.full_like(inp["dt_bias"], bias)
         ref_out, ref_hT = run_oracle(inp)
         out, hT = run_gpu(inp, algo)
-        check_against(out, hT, ref_out, ref_hT)
+        check_against(out, hT, ref_out, ref_hT, SATURATED_RATIO, SATURATED_RATIO)
 
 
 # ---- size-independent properties, GPU against GPU: bit-exact ----
@@ -187,17 +192,29 @@ def test_batch_rows_are_independent(algo):
         assert torch.equal(h1[0], hT[b])
 
 
-def test_out_rows_past_sequence_end_untouched_and_inputs_unmodified():
+def test_out_rows_past_sequence_end_untouched_and_inputs_unmodified(algo):
+    """The tensors hold 40 tokens, the sequences cover the first 25: the operator may not write the 15 rows of
+    ``out`` past ``cu_seqlens[-1]`` (a TMA store of a whole chunk tile would), and never writes its inputs."""
     lens = [5, 20]
-    w = Workload("u", 1, 25, 2, seq_lens=lens)
+    w = Workload("u", 1, 40, 2)
     inp = make_inputs(w, seed=6)
     d = to_device(inp, "cuda")
+    d["cu_seqlens"] = torch.tensor([0, 5, 25], dtype=torch.int64, device="cuda")
+    d["out"].fill_(7.0)
     keep = {key: d[key].clone() for key in ("q", "k", "v", "g", "beta")}
     flashkda_b200.fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["out"], A_log=d["A_log"],
-                      dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], cu_seqlens=d["cu_seqlens"])
+                      dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], cu_seqlens=d["cu_seqlens"], algo=algo)
     torch.cuda.synchronize()
     for key, val in keep.items():
         assert torch.equal(val, d[key])
+    assert (d["out"][:, sum(lens):] == 7.0).all(), "rows past the last sequence were written"
+    assert not (d["out"][:, :sum(lens)] == 7.0).all()
+    # and the covered rows equal a call on tensors cut to the covered length
+    cut = {key: d[key][:, :25].contiguous() for key in ("q", "k", "v", "g", "beta")}
+    out2 = torch.zeros_like(cut["v"])
+    flashkda_b200.fwd(cut["q"], cut["k"], cut["v"], cut["g"], cut["beta"], d["scale"], out2, A_log=d["A_log"],
+                      dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], cu_seqlens=d["cu_seqlens"], algo=algo)
+    assert torch.equal(out2, d["out"][:, :25])
 
 
 def test_host_argument_errors_on_gpu():
@@ -269,40 +286,31 @@ def test_segment_scheduling_fixed_batch():
     check_against(out[:3], hT[:3], ref_out, ref_hT)
 
 
-def test_recurrence_kernel_variants_agree(monkeypatch):
-    """The tensor-core recurrence has three kernels: three chains per CTA with the state's MMA copy in tensor
-    memory (default when there are more chains than SMs), the same with that copy in shared memory
-    (FKDA_TC_SS), and one chain per CTA with the idle warpgroups sharing the state update (few chains).
-    All three follow the same numerics."""
+def test_recurrence_kernel_variants_agree():
+    """The tensor-core recurrence has two kernels: three chains per CTA (more chains than SMs) and one chain per
+    CTA with the idle warpgroups sharing the state update (few chains).  Both issue the same tensor-core
+    products in the same order, so their results are identical."""
     lens = [700, 16, 1, 333, 2048]
     w = Workload("var", 1, sum(lens), 6, state_in="fp32", state_out="fp32", seq_lens=lens)
     inp = make_inputs(w, seed=21)
     ref_out, ref_hT = run_oracle(inp)
-    out_w, hT_w = run_gpu(inp, "tc")                       # 30 chains: the one-chain-per-CTA kernel
+    out_w, hT_w = run_gpu(inp, "tc")                                  # 30 chains: the one-chain-per-CTA kernel
     check_against(out_w, hT_w, ref_out, ref_hT)
-    monkeypatch.setenv("FKDA_TC_NO_WIDE", "1")
-    out_t, hT_t = run_gpu(inp, "tc")                       # three chains per CTA, state copy in tensor memory
-    check_against(out_t, hT_t, ref_out, ref_hT)
-    monkeypatch.setenv("FKDA_TC_SS", "1")
-    out_s, hT_s = run_gpu(inp, "tc")                       # three chains per CTA, state copy in shared memory
-    assert torch.equal(out_s, out_w) and torch.equal(hT_s, hT_w)
-    mism = (out_t != out_s).float().mean().item()
-    print(f"tensor-memory state variant vs shared-memory variant: out mismatch {mism:.3e}")
-    assert oracle.err_ratio(out_t, out_s) <= 2e-3
-    assert oracle.err_ratio(hT_t, hT_s) <= 1e-3
-    # bf16 states and the segment queue (more than 444 chains) through both variants
+    out_t, hT_t = run_gpu(inp, "tc", flags=_lib.FLAG_NO_WIDE)         # three chains per CTA
+    assert torch.equal(out_t, out_w) and torch.equal(hT_t, hT_w)
+    # bf16 states and the segment queue (more than 444 chains), with two forced segment lengths
     lens2 = torch.randint(1, 1500, (80,), generator=torch.Generator().manual_seed(3)).tolist()
     w2 = Workload("var2", 1, sum(lens2), 6, state_in="bf16", state_out="bf16", seq_lens=lens2)
     inp2 = make_inputs(w2, seed=22)
-    out_s2, hT_s2 = run_gpu(inp2, "tc")
-    monkeypatch.delenv("FKDA_TC_SS")
-    out_t2, hT_t2 = run_gpu(inp2, "tc")
-    assert oracle.err_ratio(out_t2, out_s2) <= 2e-3
-    assert oracle.err_ratio(hT_t2, hT_s2) <= 1e-3
+    out_a, hT_a = run_gpu(inp2, "tc")
+    out_b, hT_b = run_gpu(inp2, "tc", flags=_lib.flags_seg_chunks(8))
+    out_c, hT_c = run_gpu(inp2, "tc", flags=_lib.flags_seg_chunks(40))
+    assert torch.equal(out_a, out_b) and torch.equal(hT_a, hT_b)
+    assert torch.equal(out_a, out_c) and torch.equal(hT_a, hT_c)
 
 
 @pytest.mark.parametrize("B,T,H", [(1, 8192, 8), (2, 2100, 4), (1, 1030, 32)])
-def test_slab_pipeline_matches_single_pass(B, T, H, monkeypatch):
+def test_slab_pipeline_matches_single_pass(B, T, H):
     """Few chains on a fixed batch: the forward runs as slabs of chunks, the prepare stage of the next slab on the
     idle SMs (side stream) while the recurrence walks the current one, chain states handed from slab to slab.
     Same kernels, same numbers as the two-launch form."""
@@ -310,8 +318,7 @@ def test_slab_pipeline_matches_single_pass(B, T, H, monkeypatch):
     inp = make_inputs(w, seed=31)
     out_p, hT_p = run_gpu(inp, "tc")
     n_pipe = flashkda_b200.last_launch_count()
-    monkeypatch.setenv("FKDA_TC_NO_SLABS", "1")
-    out_s, hT_s = run_gpu(inp, "tc")
+    out_s, hT_s = run_gpu(inp, "tc", flags=_lib.FLAG_NO_SLABS)
     assert flashkda_b200.last_launch_count() == 2 and n_pipe in (4, 8)
     assert torch.equal(out_p, out_s) and torch.equal(hT_p, hT_s)
     if T <= 2100:

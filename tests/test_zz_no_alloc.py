@@ -48,13 +48,35 @@ def test_noalloc_matches_regular_entry_point_twice(algo):
     stream = torch.cuda.current_stream().cuda_stream
     for call in range(2):  # the second call reuses the scratch the first one left behind
         d = to_device(inp, "cuda")
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]   # the driver's count of free device memory (cudaMemGetInfo)
         rc = L.fkda_fwd_noalloc(_params(d, algo), stream)
         assert rc == 0, _lib.status_string(rc)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call == 1:  # (a first call may make the driver load kernel code; the second finds everything in place)
+            assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was taken during the call"
+        assert L.fkda_device_status(None, stream) == 0   # NULL = the built-in scratch
         assert torch.equal(d["out"], ref["out"]), f"call {call}: out differs"
         assert torch.equal(d["final_state"], ref["final_state"]), f"call {call}: final_state differs"
+
+
+@pytest.mark.gpu
+def test_noalloc_decode_step_of_a_large_batch():
+    """A decode step keeps no per-chunk records, so it fits the built-in scratch whatever the batch size."""
+    L = _lib.lib()
+    w = Workload("nadec", 640, 1, 16, state_in="bf16", state_out="bf16", lower_bound=-1.0)
+    inp = make_inputs(w, seed=5)
+    ref = to_device(inp, "cuda")
+    flashkda_b200.fwd(ref["q"], ref["k"], ref["v"], ref["g"], ref["beta"], ref["scale"], ref["out"],
+                      A_log=ref["A_log"], dt_bias=ref["dt_bias"], lower_bound=ref["lower_bound"],
+                      initial_state=ref["initial_state"], final_state=ref["final_state"])
+    d = to_device(inp, "cuda")
+    rc = L.fkda_fwd_noalloc(_params(d, "tc"), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.status_string(rc)
+    torch.cuda.synchronize()
+    assert torch.equal(d["out"], ref["out"]) and torch.equal(d["final_state"], ref["final_state"])
 
 
 @pytest.mark.gpu
