@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["fwd", "get_workspace_size", "last_launch_count", "default_algo", "device_status"]
+__all__ = ["fwd", "get_workspace_size", "last_launch_count", "default_algo", "device_status", "chunk_states_slots"]
 
 D = 128
 _ENV_ALGO = "FLASHKDA_B200_ALGO"
@@ -35,7 +35,8 @@ def _check(cond, msg):
 
 
 def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None, final_state=None,
-        cu_seqlens=None, *, algo: str = None, workspace: torch.Tensor = None, phase_mask: int = 0, flags: int = 0):
+        cu_seqlens=None, *, algo: str = None, workspace: torch.Tensor = None, phase_mask: int = 0, flags: int = 0,
+        chunk_states: torch.Tensor = None, chunk_states_every: int = 4):
     """FlashKDA forward; writes ``out`` (and ``final_state``) in place and returns ``None``.
 
     q, k, v, g, out: bf16 ``[B, T, H, 128]``; beta: bf16 ``[B, T, H]`` logits; A_log: fp32
@@ -48,6 +49,10 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
     uint8 scratch tensor of at least ``get_workspace_size(...)`` bytes.  ``phase_mask`` is a
     measurement aid (see ``fkda_fwd_params.phase_mask``) and ``flags`` selects kernel variants for tests
     (``fkda_fwd_params.flags``); leave both 0.
+
+    ``chunk_states`` (optional, bf16 ``[slots, H, 128, 128]``) receives the state of every sequence before each
+    group of ``chunk_states_every`` 16-token chunks (``chunk_states_slots`` gives the slot count); with the default
+    of 4 these are the states FLA's ``chunk_kda`` returns as ``h`` for ``return_intermediate_states=True``.
 
     The call returns without synchronising, so it cannot tell whether a kernel gave up on one of its
     bounded internal waits (possible only when other long-running kernels hold the GPU's SMs for
@@ -106,6 +111,13 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
             _check(s.dim() == 4 and tuple(s.shape) == (N, H, D, D), f"{name} must be [N, H, D, D]")
             _check(s.device == dev, f"{name} must be on the same device as q")
 
+    if chunk_states is not None:
+        _check(chunk_states.is_cuda and chunk_states.is_contiguous() and chunk_states.dtype == bf16,
+               "chunk_states must be a contiguous CUDA bfloat16 tensor")
+        _check(int(chunk_states_every) >= 1, "chunk_states_every must be >= 1")
+        _check(cu_seqlens is not None or chunk_states.numel() == chunk_states_slots(B, T, chunk_states_every) * H * D * D,
+               "chunk_states must hold B * ceil(T / (16 * every)) slots of [H, 128, 128]")
+
     L = _lib.lib()
     algo_id = _lib.ALGOS[algo or default_algo()]
     T_total = B * T
@@ -118,7 +130,8 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
         state_dtype=_lib.FKDA_STATE_FP32 if state_fp32 else _lib.FKDA_STATE_BF16, algo=algo_id,
         cu_seqlens=ptr(cu_seqlens), B=B, T=T, H=H, N=N, token_stride=H * D, beta_token_stride=H,
         scale=float(scale), lower_bound=lower_bound, workspace=None, workspace_bytes=0,
-        phase_mask=int(phase_mask), flags=int(flags))
+        phase_mask=int(phase_mask), flags=int(flags), chunk_states=ptr(chunk_states),
+        chunk_states_every=int(chunk_states_every) if chunk_states is not None else 0)
     with torch.cuda.device(dev):
         need = int(L.fkda_workspace_bytes_for(p))  # what this call's path needs (a decode step: 256 bytes)
     if workspace is None:
@@ -135,6 +148,15 @@ def fwd(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state
     # `workspace` was allocated on (or handed over for) the current stream, so the caching allocator
     # reuses it in stream order once this reference is dropped
     return None
+
+
+def chunk_states_slots(B: int, T: int, every: int = 4, seq_lens=None) -> int:
+    """Slots a ``chunk_states`` tensor needs: per sequence ``ceil(len / (16 * every))``; pass the lengths of a
+    ragged batch as ``seq_lens``."""
+    group = 16 * int(every)
+    if seq_lens is not None:
+        return int(sum((int(x) + group - 1) // group for x in seq_lens))
+    return int(B) * ((int(T) + group - 1) // group)
 
 
 def device_status(workspace: torch.Tensor) -> int:

@@ -32,6 +32,7 @@ class FwdParams(ctypes.Structure):
         ("scale", ctypes.c_float), ("lower_bound", ctypes.c_double),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("phase_mask", ctypes.c_int32), ("flags", ctypes.c_int32),
+        ("chunk_states", ctypes.c_void_p), ("chunk_states_every", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -47,6 +48,10 @@ def lib():
                 f"{LIB_PATH} is missing: build it with `python -m flashkda_b200.build` "
                 "(flashkda_b200 has no CPU or PyTorch fallback)")
         L = ctypes.CDLL(LIB_PATH)
+        L.fkda_params_size.restype = ctypes.c_size_t
+        if L.fkda_params_size() != ctypes.sizeof(FwdParams):
+            raise RuntimeError(f"{LIB_PATH} was built from another revision of include/flashkda_b200.h "
+                               f"(struct of {L.fkda_params_size()} bytes, binding has {ctypes.sizeof(FwdParams)}): rebuild it")
         L.fkda_fwd.restype = ctypes.c_int
         L.fkda_fwd.argtypes = [ctypes.POINTER(FwdParams), ctypes.c_void_p]
         L.fkda_workspace_bytes.restype = ctypes.c_size_t

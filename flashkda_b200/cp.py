@@ -9,14 +9,14 @@ One chunk of the recurrence is affine in the state: with the state kept as S[V, 
 forward operator yields directly: ``N`` is the final state of the shard started from zero, ``M`` is
 the final state of the same shard run with ``v = 0`` from the identity.  So
 
-  1. rank 0 runs its shard for real (its final state is exact); ranks 1 .. G-2 compute (M_r, N_r)
-     with two forward calls on two CUDA streams (a single sequence leaves most of the GPU idle, so
-     the two calls overlap); the last rank needs no map;
+  1. rank 0 runs its shard for real (its final state is exact); ranks 1 .. G-2 compute (M_r, N_r):
+     the prepare stage once, then two recurrences over the same chunk records (the records depend on
+     q, k, g, beta only); the last rank needs no map;
   2. one all-gather (torch.distributed: NCCL over NVLink on GPUs, gloo in CPU tests) of the fp32
      pairs, 2 * H * 128 * 128 * 4 bytes per rank;
   3. every rank folds its predecessors in order, ``S <- S @ M_j + N_j`` (fp32), to get its true
-     initial state, then runs the ordinary forward on its shard; the last rank's final state is the
-     sequence's final state.
+     initial state, then walks its records once more from that state; the last rank's final state is
+     the sequence's final state.
 
 Shard boundaries must be multiples of 16 tokens (every shard but the last), so that the chunk grid
 of the sharded run equals that of the one-shot run.  The maps carry the bf16 roundings of the
@@ -72,54 +72,101 @@ def fold_initial_state(first_end_state: torch.Tensor, maps: List[Tuple[torch.Ten
     return S
 
 
+def _shard_argument_error(q, k, v, g, beta, out, initial_state, final_state, rank, world):
+    if q.dim() != 4 or q.shape[0] != 1:
+        return "context parallelism shards ONE sequence: q must be [1, T, H, 128]"
+    for name, t in (("k", k), ("v", v), ("g", g), ("out", out)):
+        if tuple(t.shape) != tuple(q.shape):
+            return f"{name} must match q shape"
+    if tuple(beta.shape) != tuple(q.shape[:3]):
+        return "beta must be [1, T, H] matching q"
+    if rank < world - 1 and q.shape[1] % 16 != 0:
+        return "every shard but the last must hold a multiple of 16 tokens"
+    H = q.shape[2]
+    for name, s in (("initial_state", initial_state), ("final_state", final_state)):
+        if s is not None:
+            if tuple(s.shape) != (1, H, D, D):
+                return f"{name} must be [1, H, 128, 128]"
+            if s.dtype not in (torch.bfloat16, torch.float32):
+                return f"{name} must be bfloat16 or float32"
+    return None
+
+
+def _check_shard_arguments(q, k, v, g, beta, out, initial_state, final_state, rank, world, group):
+    """Argument checks, agreed on by ALL ranks before the data-path collectives: a shard can be wrong on one rank
+    only (its length, a state dtype), and a rank that raised alone would leave the others waiting inside the
+    all-gather.  One 4-byte all-reduce carries the verdict; every rank raises when any rank found a fault."""
+    import torch.distributed as dist
+    err = _shard_argument_error(q, k, v, g, beta, out, initial_state, final_state, rank, world)
+    if world > 1:
+        flag = torch.tensor([0 if err is None else 1], dtype=torch.int32, device=q.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+        if int(flag.item()) != 0 and err is None:
+            err = "another rank of the group rejected its arguments"
+    if err is not None:
+        raise RuntimeError(err)
+
+
 def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None,
                          final_state=None, group=None, fwd_fn: Callable = None, parts: int = 1):
     """Forward over one sequence sharded across the ranks of ``group`` (contiguous shards in rank
-    order, B = 1, every shard but the last a multiple of 16 tokens).  ``initial_state`` is used by
-    rank 0; ``final_state`` (optional, any rank) receives the state after the last token.
-    Writes this rank's ``out`` in place."""
+    order, B = 1, every shard but the last a multiple of 16 tokens).  ``initial_state`` (bf16 or fp32) is
+    used by rank 0; ``final_state`` (optional, any rank, either dtype) receives the state after the last
+    token.  Writes this rank's ``out`` in place.
+
+    With the device operator (``fwd_fn`` left None) every rank prepares its chunk records ONCE and runs its
+    recurrences over them (the maps ``N`` and ``M``, then the real pass), and ``parts`` > 1 additionally
+    splits the rank's shard into that many pieces that run side by side (``SequenceSplit``).  A caller-given
+    ``fwd_fn`` (tests: the CPU oracle) is called with the reference signature only."""
     import torch.distributed as dist
-    if fwd_fn is None:
-        from . import fwd as fwd_fn
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    assert q.shape[0] == 1, "context parallelism shards ONE sequence (B must be 1)"
-    if rank < world - 1:
-        assert q.shape[1] % 16 == 0, "every shard but the last must hold a multiple of 16 tokens"
+    _check_shard_arguments(q, k, v, g, beta, out, initial_state, final_state, rank, world, group)
     H, dev = q.shape[2], q.device
     payload = torch.zeros(2, 1, H, D, D, dtype=torch.float32, device=dev)
-    if parts > 1:
-        # every rank also splits its own shard into `parts` pieces (SequenceSplit): all ranks compute their
-        # composed map in parallel, exchange, fold, and finish from their true initial state
+    S0 = None if initial_state is None else initial_state.to(torch.float32)   # maps and folds are fp32
+    last = world - 1
+    src_last = dist.get_global_rank(group, last) if group is not None else last
+
+    def publish_final(end):
+        if final_state is not None:
+            buf = end.contiguous() if rank == last else torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
+            if world > 1:
+                dist.broadcast(buf, src=src_last, group=group)
+            final_state.copy_(buf.to(final_state.dtype))
+
+    if fwd_fn is None:
+        # ---- device operator: chunk records prepared once per rank, reused by every recurrence ----
+        if parts > 1 and q.shape[1] % (16 * parts) != 0:
+            parts = 1   # (this rank only; the exchange does not depend on how a rank walks its own shard)
         split = SequenceSplit(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, parts)
-        if world > 1:
+        end = None
+        if world == 1 or rank == 0:
+            end = split.finish(S0 if rank == 0 else None, None)   # exact for this shard's true initial state
+            payload[1].copy_(end)
+        elif rank < last:
             Mt, Nt = split.maps()
             payload[0].copy_(Mt)
             payload[1].copy_(Nt)
+        elif parts > 1:
+            split.maps(total=False)   # the last rank needs the maps of its own pieces only
+        if world > 1:
             gathered = [torch.empty_like(payload) for _ in range(world)]
             dist.all_gather(gathered, payload, group=group)
-            S_in = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev) if initial_state is None \
-                else initial_state.to(torch.float32)
-            for j in range(rank):
-                S_in = torch.matmul(S_in, gathered[j][0]) + gathered[j][1]
-        else:
-            S_in = initial_state
-        end = split.finish(S_in, None)
-        if final_state is not None:
-            buf = end.contiguous() if rank == world - 1 else torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
-            if world > 1:
-                dist.broadcast(buf, src=dist.get_global_rank(group, world - 1) if group is not None else world - 1,
-                               group=group)
-            final_state.copy_(buf.to(final_state.dtype))
+            if rank > 0:
+                S_in = fold_initial_state(gathered[0][1], [(gathered[j][0], gathered[j][1]) for j in range(1, rank)])
+                end = split.finish(S_in, None)
+        publish_final(end)
         return
+
+    # ---- any operator with the reference signature (CPU tests run the oracle here) ----
     if world == 1:
         fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, final_state, None)
         return
     if rank == 0:
         end = payload[1]
-        fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state, end, None)
-    elif rank < world - 1:
-        streams = (torch.cuda.Stream(dev), torch.cuda.Stream(dev)) if dev.type == "cuda" else None
-        M, N = shard_maps(fwd_fn, q, k, v, g, beta, scale, A_log, dt_bias, lower_bound, True, streams)
+        fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, S0, end, None)
+    elif rank < last:
+        M, N = shard_maps(fwd_fn, q, k, v, g, beta, scale, A_log, dt_bias, lower_bound, True, None)
         payload[0].copy_(M)
         payload[1].copy_(N)
     gathered = [torch.empty_like(payload) for _ in range(world)]
@@ -127,13 +174,9 @@ def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bou
     last_state = None
     if rank > 0:
         S_in = fold_initial_state(gathered[0][1], [(gathered[j][0], gathered[j][1]) for j in range(1, rank)])
-        if rank == world - 1:
-            last_state = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
+        last_state = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev)
         fwd_fn(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, S_in.contiguous(), last_state, None)
-    if final_state is not None:
-        buf = last_state if rank == world - 1 else torch.empty(1, H, D, D, dtype=torch.float32, device=dev)
-        dist.broadcast(buf, src=dist.get_global_rank(group, world - 1) if group is not None else world - 1, group=group)
-        final_state.copy_(buf.to(final_state.dtype))
+    publish_final(last_state)
 
 
 def fwd_sharded_emulated(n_shards: int, q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound,
@@ -180,28 +223,37 @@ class SequenceSplit:
     def __init__(self, q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, parts: int):
         import flashkda_b200 as F
         B, T, H, _ = q.shape
-        assert B == 1 and T % (16 * parts) == 0, "T must be a multiple of 16 * parts"
+        assert B == 1 and (parts == 1 or T % (16 * parts) == 0), "T must be a multiple of 16 * parts"
         self.F, self.P, self.H, self.dev = F, parts, H, q.device
         vw = lambda x: x.view(parts, T // parts, *x.shape[2:])
         self.t = (vw(q), vw(k), vw(v), vw(g), vw(beta))
         self.out = vw(out)
         self.args = (A_log, dt_bias, lower_bound)
         self.scale = scale
-        self.ws = torch.empty(max(1, F.get_workspace_size(T, H, parts)), dtype=torch.uint8, device=self.dev)
+        self.ws = torch.empty(max(256, F.get_workspace_size(T, H, parts)), dtype=torch.uint8, device=self.dev)
         self.M = self.N = None
+        self.prepared = False   # whether self.ws holds the chunk records of this shard
 
-    def maps(self):
-        """Per-piece maps (kept) and the composed map of the whole sequence ``(M_total, N_total)``."""
+    def _fwd(self, v, h0, hT):
+        """One operator call on the batch of pieces; the first one also runs the prepare stage, later ones
+        walk the records it left in the workspace."""
         from . import _lib
+        qb, kb, _, gb, bb = self.t
+        self.F.fwd(qb, kb, v, gb, bb, self.scale, self.out, *self.args, h0, hT, None, workspace=self.ws,
+                   phase_mask=_lib.PHASE_RECURRENCE if self.prepared else 0)
+        self.prepared = True
+
+    def maps(self, total: bool = True):
+        """Per-piece maps (kept) and, with ``total``, the composed map of the whole shard ``(M, N)``."""
         P, H, dev = self.P, self.H, self.dev
-        qb, kb, vb, gb, bb = self.t
+        vb = self.t[2]
         self.N = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
         self.M = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
         eye = torch.eye(D, dtype=torch.float32, device=dev).expand(P, H, D, D).contiguous()
-        # pass 1a: prepare + recurrence from zero (N);  pass 1b: recurrence only, v = 0 from the identity (M)
-        self.F.fwd(qb, kb, vb, gb, bb, self.scale, self.out, *self.args, None, self.N, None, workspace=self.ws)
-        self.F.fwd(qb, kb, torch.zeros_like(vb), gb, bb, self.scale, self.out, *self.args, eye, self.M, None,
-                   workspace=self.ws, phase_mask=_lib.PHASE_RECURRENCE)
+        self._fwd(vb, None, self.N)                       # from zero: N
+        self._fwd(torch.zeros_like(vb), eye, self.M)      # v = 0 from the identity: M
+        if not total:
+            return None, None
         Mt, Nt = self.M[0:1], self.N[0:1]
         for p in range(1, P):
             Nt = torch.matmul(Nt, self.M[p:p + 1]) + self.N[p:p + 1]
@@ -209,12 +261,11 @@ class SequenceSplit:
         return Mt, Nt
 
     def finish(self, initial_state=None, final_state=None):
-        """Fold the pieces from ``initial_state`` and run the batch for real (writes ``out``)."""
-        from . import _lib
-        if self.M is None:
-            self.maps()
+        """Fold the pieces from ``initial_state`` and run the batch for real (writes ``out``); returns the
+        state after the last token, fp32 ``[1, H, 128, 128]``."""
         P, H, dev = self.P, self.H, self.dev
-        qb, kb, vb, gb, bb = self.t
+        if P > 1 and self.M is None:
+            self.maps(total=False)
         S = torch.zeros(1, H, D, D, dtype=torch.float32, device=dev) if initial_state is None \
             else initial_state.to(torch.float32)
         h0 = torch.empty(P, H, D, D, dtype=torch.float32, device=dev)
@@ -223,8 +274,7 @@ class SequenceSplit:
             if p + 1 < P:
                 S = torch.matmul(S, self.M[p:p + 1]) + self.N[p:p + 1]
         hT = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
-        self.F.fwd(qb, kb, vb, gb, bb, self.scale, self.out, *self.args, h0, hT, None, workspace=self.ws,
-                   phase_mask=_lib.PHASE_RECURRENCE)
+        self._fwd(self.t[2], h0, hT)
         if final_state is not None:
             final_state.copy_(hT[P - 1:P].to(final_state.dtype))
         return hT[P - 1:P]

@@ -10,7 +10,9 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 extern "C" {
 
-int fkda_version(void) { return 1000; }
+int fkda_version(void) { return 1001; }
+
+size_t fkda_params_size(void) { return sizeof(fkda_fwd_params); }
 
 const char* fkda_status_string(int status) {
     switch (status) {
@@ -76,6 +78,7 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
     if (p->cu_seqlens == nullptr && p->N != p->B) return FKDA_ERR_BAD_SHAPE;
     if (p->token_stride < p->H * FKDA_HEAD_DIM || p->beta_token_stride < p->H) return FKDA_ERR_BAD_SHAPE;
     if (p->state_dtype != FKDA_STATE_BF16 && p->state_dtype != FKDA_STATE_FP32) return FKDA_ERR_BAD_STATE_DTYPE;
+    if (p->chunk_states != nullptr && (p->chunk_states_every < 1 || !aligned16(p->chunk_states))) return FKDA_ERR_BAD_SHAPE;
     if (!p->A_log || !p->dt_bias) return FKDA_ERR_NULL_POINTER;
     const int64_t T_total = p->B * p->T;
     if (T_total > 0 && (!p->q || !p->k || !p->v || !p->g || !p->beta || !p->out)) return FKDA_ERR_NULL_POINTER;
@@ -92,7 +95,7 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
     int launches = 0;
     int rc;
-    if (algo == FKDA_ALGO_TC && fkda::decode_eligible(*p) && !(p->flags & FKDA_FLAG_NO_DECODE))
+    if (algo == FKDA_ALGO_TC && fkda::decode_eligible(*p) && !(p->flags & FKDA_FLAG_NO_DECODE) && p->chunk_states == nullptr)
         rc = fkda::launch_decode(*p, stream, &launches);  // one token per sequence: state read-modify-write
     else if (algo == FKDA_ALGO_TC)
         rc = fkda::launch_tc(*p, stream, &launches);

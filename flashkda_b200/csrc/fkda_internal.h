@@ -34,6 +34,9 @@ struct TwoPassArgs {
     int64_t T, H, N, total_tiles;
     int64_t token_stride, beta_token_stride;
     float scale, gate_scale;
+    __nv_bfloat16* chunk_states;   // optional export of the state before every cs_every-th chunk (see fkda_fwd_params)
+    const int32_t* cs_prefix;      // [N] first export slot of every sequence (varlen; fixed batches compute it)
+    int32_t cs_every;
     uint64_t wait_ns;      // limit of every bounded device-side wait (mbarrier, queue slot)
     bool state_fp32;
     bool test_drop_push;   // test hook (FKDA_FLAG_TEST_DROP_PUSH): finished segments do not queue their follow-up
@@ -44,8 +47,8 @@ struct TwoPassArgs {
 //   [256, ..) tile prefix (N + 1 int32, padded to 256 B)
 //   then      H * total_tiles records
 constexpr size_t kWsHeaderBytes = 256;
-// (N + 1) prefix entries followed by N entries of the length order
-inline size_t ws_prefix_bytes(int64_t N) { return (size_t)(((2 * N + 1) * 4 + 255) / 256 * 256); }
+// (N + 1) chunk-prefix entries, N entries of the length order, N + 1 entries of the state-export prefix
+inline size_t ws_prefix_bytes(int64_t N) { return (size_t)(((3 * N + 2) * 4 + 255) / 256 * 256); }
 constexpr int64_t kSeqOrderMaxN = 512;  // beyond this the quadratic ranking in the prefix kernel is not worth its time
 inline int64_t ws_tiles_upper_bound(int64_t T_total, int64_t N) { return (T_total + 15) / 16 + N; }
 
@@ -65,6 +68,13 @@ int launch_decode(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches
 // Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
 // workspace carving).
 void fill_args(const fkda_fwd_params& p, TwoPassArgs* a);
-void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, cudaStream_t stream);
+void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
+                        int cs_tokens, cudaStream_t stream);
+// First state-export slot of sequence n.
+__device__ __forceinline__ int64_t cs_first_slot(const TwoPassArgs& a, int64_t n) {
+    if (a.cu_seqlens != nullptr) return a.cs_prefix[n];
+    const int64_t group = 16 * (int64_t)a.cs_every;
+    return n * ((a.T + group - 1) / group);
+}
 
 }  // namespace fkda

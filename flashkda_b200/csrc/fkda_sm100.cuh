@@ -48,7 +48,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after `limit_ns` of wall time (or when *abort_flag becomes non-zero)
 // and returns false; the caller then records an error and leaves through the common exit path.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint64_t limit_ns = 2000000000ull) {
+                                                  uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
@@ -186,6 +186,28 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, uint32_t r0, uint32_t r
                  : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Fragment-shaped accesses: a warp touches 16 TMEM lanes starting at the lane field of taddr (a multiple of 16
+// inside the warp's own quadrant of 32).  Thread i = 4 g + t of the warp:
+//   16x256b.x2 load:  r0,r1 = (lane g, columns 2t, 2t+1)   r2,r3 = (lane g+8, same columns)
+//                     r4,r5 = (lane g, columns 2t+8, 2t+9) r6,r7 = (lane g+8, same columns)
+//     i.e. 16 fp32 columns arrive as the accumulator fragments of two mma.sync m16n8 tiles;
+//   16x128b.x2 store: r0 -> (lane g, column t), r1 -> (lane g+8, column t), r2 -> (lane g, column t+4),
+//                     r3 -> (lane g+8, column t+4)
+//     i.e. the A fragment {a0,a1,a2,a3} of an mma.sync m16n8k16 (16 rows x 16 bf16 = 8 packed columns) lands as
+//     a K-major tcgen05.mma A operand.
+// (Both mappings were read back on a B200 with a pattern-filling probe.)
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x128b_x2(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2),
+                 "r"(r3)
+                 : "memory");
+}
 
 // ------------------------------------------------------------ tcgen05.mma ----
 // Shared-memory matrix descriptor, no swizzle ("interleaved" canonical layouts), 16-byte units:

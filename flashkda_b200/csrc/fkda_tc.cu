@@ -62,6 +62,7 @@ struct TcChain {
     int64_t seq_len;
     int n_chunks;
     const uint8_t* rec_base;  // record of the chain's chunk 0
+    int64_t cs_slot0;         // first state-export slot of the sequence (valid when chunk_states is given)
 };
 __device__ __forceinline__ TcChain tc_locate_chain(const TwoPassArgs& a, int64_t chain) {
     TcChain c;
@@ -81,6 +82,7 @@ __device__ __forceinline__ TcChain tc_locate_chain(const TwoPassArgs& a, int64_t
     }
     c.n_chunks = (int)((c.seq_len + kChunk - 1) / kChunk);
     c.rec_base = a.workspace + ((int64_t)c.h * a.total_tiles + tile_base) * (int64_t)kTcRecord;
+    c.cs_slot0 = a.chunk_states != nullptr ? cs_first_slot(a, c.n) : 0;
     return c;
 }
 
@@ -294,7 +296,7 @@ static TcCarve tc_carve(const fkda_fwd_params& p, int sms) {
     return c;
 }
 size_t tc_workspace_bytes_for(const fkda_fwd_params& p) {
-    if (decode_eligible(p) && !(p.flags & FKDA_FLAG_NO_DECODE)) return kWsHeaderBytes;  // status word only
+    if (decode_eligible(p) && !(p.flags & FKDA_FLAG_NO_DECODE) && p.chunk_states == nullptr) return kWsHeaderBytes;  // status word only
     const TcCarve c = tc_carve(p, device_sm_count());
     return kWsHeaderBytes + ws_prefix_bytes(p.N) + c.slots + c.states + c.records;
 }
@@ -361,7 +363,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         (!encode_token_map(&maps.v, p.v, T_total, p.H, p.token_stride) ||
          !encode_token_map(&maps.out, p.out, T_total, p.H, p.token_stride)))
         return FKDA_ERR_LAUNCH;
-    const int wide_smem = kWideCtrlOff + (int)sizeof(TcWideCtrl) + 128;
+    const int wide_smem = kWideSmemBytes;
     if (do_rec && wide &&
         cudaFuncSetAttribute(recurrence_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem) != cudaSuccess)
         return FKDA_ERR_LAUNCH;
@@ -410,7 +412,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         for (int i = 0; i < n_slabs; ++i) {
             if (bounds[i + 1] <= bounds[i]) continue;
             if (i > 0 && cudaStreamWaitEvent(stream, ss->done[i], 0) != cudaSuccess) return FKDA_ERR_LAUNCH;
-            recurrence_tc_wide_kernel<<<(unsigned)chains, 384, wide_smem, stream>>>(slab_args(i), maps);
+            recurrence_tc_wide_kernel<<<(unsigned)chains, kWideThreads, wide_smem, stream>>>(slab_args(i), maps);
             ++launches;
         }
         if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
@@ -419,7 +421,8 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     }
 
     if (varlen && do_prep) {
-        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order), stream);
+        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order),
+                           a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every, stream);
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {
@@ -432,7 +435,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
         if (ctas < 1) ctas = 1;
         if (wide) {
             // few chains: one per CTA, the idle warpgroups help with the state update
-            recurrence_tc_wide_kernel<<<(unsigned)ctas, 384, wide_smem, stream>>>(a, maps);
+            recurrence_tc_wide_kernel<<<(unsigned)ctas, kWideThreads, wide_smem, stream>>>(a, maps);
         } else {
             // three chains per CTA, state copy and 16-deep A operands in tensor memory
             if (cudaFuncSetAttribute(recurrence_tc_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmemBytes) !=

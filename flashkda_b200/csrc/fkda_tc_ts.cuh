@@ -158,6 +158,14 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
             uint8_t* st = cs + kTsStage + s * kTcStageBytes;
             const uint32_t st_addr = smem_u32(st);
 
+            // ---- optional export: the state before this group of chunks (my row, bf16) ----
+            if (a.chunk_states != nullptr && t % a.cs_every == 0) {
+                uint4* dst = reinterpret_cast<uint4*>(a.chunk_states + ((ch.cs_slot0 + t / a.cs_every) * a.H + h) * (int64_t)(kD * kD) +
+                                                      (int64_t)v * kD);
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    dst[i] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
+            }
             // ---- operands of chunk t have landed ----
             if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, a.wait_ns)) { failed = true; break; }
             full_phase[s] ^= 1u;

@@ -20,33 +20,40 @@ namespace fkda {
 // Also ranks the sequences by decreasing length (order[rank] = sequence; ties by index) when the batch is small
 // enough for the quadratic count: the recurrence starts the longest chains first and keeps them apart.
 __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __restrict__ cu, int64_t N,
-                                                           int32_t* __restrict__ prefix, int32_t* __restrict__ order) {
+                                                           int32_t* __restrict__ prefix, int32_t* __restrict__ order,
+                                                           int32_t* __restrict__ cs_prefix, int cs_tokens) {
     __shared__ int64_t part[1024];
     const int tid = threadIdx.x;
     const int64_t per = (N + 1023) / 1024;
     const int64_t lo = tid * per, hi = (lo + per < N) ? lo + per : N;
-    int64_t s = 0;
-    for (int64_t n = lo; n < hi; ++n) {
-        int64_t len = cu[n + 1] - cu[n];
-        if (len < 0) len = 0;
-        s += (len + kChunk - 1) / kChunk;
-    }
-    part[tid] = s;
-    __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {
-        int64_t add = (tid >= off) ? part[tid - off] : 0;
+    // exclusive prefix over the sequences of ceil(len / unit): chunks (unit 16), or state-export groups
+    auto scan = [&](int64_t unit, int32_t* out) {
+        int64_t s = 0;
+        for (int64_t n = lo; n < hi; ++n) {
+            int64_t len = cu[n + 1] - cu[n];
+            if (len < 0) len = 0;
+            s += (len + unit - 1) / unit;
+        }
         __syncthreads();
-        part[tid] += add;
+        part[tid] = s;
         __syncthreads();
-    }
-    int64_t run = (tid == 0) ? 0 : part[tid - 1];
-    for (int64_t n = lo; n < hi; ++n) {
-        prefix[n] = (int32_t)run;
-        int64_t len = cu[n + 1] - cu[n];
-        if (len < 0) len = 0;
-        run += (len + kChunk - 1) / kChunk;
-    }
-    if (tid == 1023) prefix[N] = (int32_t)part[1023];
+        for (int off = 1; off < 1024; off <<= 1) {
+            int64_t add = (tid >= off) ? part[tid - off] : 0;
+            __syncthreads();
+            part[tid] += add;
+            __syncthreads();
+        }
+        int64_t run = (tid == 0) ? 0 : part[tid - 1];
+        for (int64_t n = lo; n < hi; ++n) {
+            out[n] = (int32_t)run;
+            int64_t len = cu[n + 1] - cu[n];
+            if (len < 0) len = 0;
+            run += (len + unit - 1) / unit;
+        }
+        if (tid == 1023) out[N] = (int32_t)part[1023];
+    };
+    scan(kChunk, prefix);
+    if (cs_prefix != nullptr) scan(cs_tokens, cs_prefix);
     if (order != nullptr) {
         for (int64_t n = tid; n < N; n += 1024) {
             const int64_t len_n = cu[n + 1] - cu[n];
@@ -115,6 +122,10 @@ __global__ void __launch_bounds__(128) recurrence_kernel(TwoPassArgs a) {
         const int len = (int)min((int64_t)kChunk, seq_len - t * kChunk);
         const uint8_t* ws = a.workspace + ((int64_t)h * a.total_tiles + tile_base + t) * (int64_t)kWsRecord;
         __syncthreads();  // previous chunk's readers are done with the operand tiles
+        if (a.chunk_states != nullptr && t % a.cs_every == 0) {   // export the state before this group of chunks
+            __nv_bfloat16* dst = a.chunk_states + ((cs_first_slot(a, n) + t / a.cs_every) * a.H + h) * (int64_t)(kD * kD) + (int64_t)v * kD;
+            for (int c = 0; c < kD; ++c) dst[c] = sm.S[v][c];
+        }
         // ---- stage the chunk operands as fp32 ----
         for (int e = v; e < kChunk * kD; e += 128) {
             const int r = e >> 7, c = e & 127;
@@ -214,8 +225,9 @@ __global__ void __launch_bounds__(128) recurrence_kernel(TwoPassArgs a) {
 // ---------------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------------
-void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, cudaStream_t stream) {
-    tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix, seq_order);
+void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
+                        int cs_tokens, cudaStream_t stream) {
+    tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix, seq_order, cs_prefix, cs_tokens);
 }
 
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
@@ -246,6 +258,8 @@ void fill_args(const fkda_fwd_params& p, TwoPassArgs* out) {
     a.gate_scale = (float)(p.lower_bound * 1.4426950408889634);  // log2-domain gate (csrc/flash_kda.cpp:128)
     const uint64_t wait_ms = (uint64_t)((p.flags >> 16) & 0x3fff);
     a.wait_ns = (wait_ms ? wait_ms : 2000u) * 1000000ull;
+    a.chunk_states = reinterpret_cast<__nv_bfloat16*>(p.chunk_states);
+    a.cs_every = p.chunk_states != nullptr ? p.chunk_states_every : 1;
     a.test_drop_push = (p.flags & FKDA_FLAG_TEST_DROP_PUSH) != 0;
     const int64_t T_total = p.B * p.T;
     const bool varlen = p.cu_seqlens != nullptr;
@@ -260,6 +274,7 @@ void fill_args(const fkda_fwd_params& p, TwoPassArgs* out) {
     a.slab_chunks = 0;
     a.tile_prefix = reinterpret_cast<int32_t*>(base + kWsHeaderBytes);
     a.seq_order = (varlen && p.N <= kSeqOrderMaxN) ? a.tile_prefix + (p.N + 1) : nullptr;
+    a.cs_prefix = a.tile_prefix + (2 * p.N + 1);
     a.workspace = base + kWsHeaderBytes + ws_prefix_bytes(p.N);
 }
 
@@ -272,7 +287,8 @@ int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launche
     const bool do_prep = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_PREPARE);
     const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
     if (varlen && do_prep) {
-        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order), stream);
+        launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order),
+                           a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every, stream);
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {

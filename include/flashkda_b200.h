@@ -85,6 +85,15 @@ typedef struct fkda_fwd_params {
                                   bit set of FKDA_PHASE_* to launch (the workspace must then already hold
                                   what the skipped phases produce) */
     int32_t flags;             /* 0 for normal use; FKDA_FLAG_* bits select kernel variants for tests and tuning */
+    void* chunk_states;        /* optional bf16 [slots, H, 128 (V), 128 (K)]: the state of every sequence BEFORE each group
+                                  of `chunk_states_every` chunks (16 * every tokens), i.e. before tokens 0, 16*every,
+                                  2*16*every, ... of the sequence; a sequence of L tokens fills ceil(L / (16*every))
+                                  consecutive slots, sequences follow each other in order (fixed batches: every
+                                  sequence ceil(T / (16*every)) slots).  NULL = not exported.  This is what FLA's
+                                  chunk_kda returns as `h` with return_intermediate_states (chunk size 64: every = 4);
+                                  the reference operator has no such output. */
+    int32_t chunk_states_every; /* >= 1 when chunk_states is given */
+    int32_t reserved;
 } fkda_fwd_params;
 
 /* fkda_fwd_params.flags.  All zero is the production setting. */
@@ -153,7 +162,10 @@ int fkda_fwd_noalloc(const fkda_fwd_params* p, void* stream);
 size_t fkda_noalloc_scratch_bytes(void);
 
 /* Library ABI version (major * 1000 + minor). */
-int fkda_version(void);
+int fkda_version(void);   /* 1001: fkda_fwd_params gained chunk_states, chunk_states_every */
+
+/* sizeof(fkda_fwd_params) as compiled into the loaded library: a binding checks its own struct against it. */
+size_t fkda_params_size(void);
 
 /* Static, human-readable name of a status code. */
 const char* fkda_status_string(int status);

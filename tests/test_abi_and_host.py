@@ -33,7 +33,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_version_status_and_workspace_size():
     L = _lib.lib()
-    assert L.fkda_version() >= 1000
+    assert L.fkda_version() >= 1001
     assert _lib.status_string(0) == "ok"
     assert "NULL" in _lib.status_string(1)
     # same growth law as the reference's get_workspace_size: 13824 B per (head, chunk) record
@@ -45,7 +45,8 @@ def test_version_status_and_workspace_size():
 
 def test_params_struct_matches_header_layout():
     # 13 pointers/ints of 8 bytes before B..., natural alignment: guards against silent drift
-    assert ctypes.sizeof(_lib.FwdParams) == 10 * 8 + 2 * 4 + 8 + 6 * 8 + 4 + 4 + 8 + 8 + 8 + 8
+    assert ctypes.sizeof(_lib.FwdParams) == 10 * 8 + 2 * 4 + 8 + 6 * 8 + 4 + 4 + 8 + 8 + 8 + 8 + 8 + 4 + 4
+    assert _lib.lib().fkda_params_size() == ctypes.sizeof(_lib.FwdParams)
 
 
 def test_null_and_shape_errors_without_gpu():

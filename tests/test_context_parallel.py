@@ -32,7 +32,7 @@ def _free_port():
     return port
 
 
-def _cp_worker(rank, world, port, T, H, seed, ret):
+def _cp_worker(rank, world, port, T, H, seed, ret, state_dtype=torch.float32):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -44,8 +44,8 @@ def _cp_worker(rank, world, port, T, H, seed, ret):
     out = torch.zeros_like(sh["v"])
     hT = torch.zeros_like(inp["final_state"])
     cp.fwd_context_parallel(sh["q"], sh["k"], sh["v"], sh["g"], sh["beta"], inp["scale"], out, inp["A_log"],
-                            inp["dt_bias"], inp["lower_bound"], initial_state=inp["initial_state"], final_state=hT,
-                            fwd_fn=oracle.fwd)
+                            inp["dt_bias"], inp["lower_bound"], initial_state=inp["initial_state"].to(state_dtype),
+                            final_state=hT, fwd_fn=oracle.fwd)
     ret[rank] = (lo, hi, out, hT)
     dist.barrier()
     dist.destroy_process_group()
@@ -69,6 +69,43 @@ def test_context_parallel_gloo(world):
     # rank 0's shard is computed exactly as in the one-shot run
     lo, hi, o, _ = ret[0]
     assert torch.equal(o, ref_out[:, lo:hi])
+
+
+def test_context_parallel_gloo_bf16_initial_state():
+    """A bf16 initial state with an fp32 final state: rank 0 widens it (the maps and folds are fp32), so no rank
+    fails an operator dtype check while the others sit in the all-gather."""
+    T, H, seed, world = 256, 1, 33, 2
+    inp = _weak_decay_inputs(T, H, seed)
+    inp["initial_state"] = inp["initial_state"].to(torch.bfloat16).float()   # what the bf16 caller means
+    ref_out, ref_hT = run_oracle(inp)
+    ret = mp.Manager().dict()
+    mp.spawn(_cp_worker, args=(world, _free_port(), T, H, seed, ret, torch.bfloat16), nprocs=world, join=True)
+    for r in range(world):
+        lo, hi, o, hT = ret[r]
+        assert oracle.err_ratio(ref_out[:, lo:hi], o) <= 1e-2
+        assert oracle.err_ratio(ref_hT, hT) <= 1e-2
+
+
+def _bad_shard_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    inp = _weak_decay_inputs(40, 1, 1)      # 40 tokens on every rank: not a multiple of 16
+    try:
+        cp.fwd_context_parallel(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["scale"], inp["out"],
+                                inp["A_log"], inp["dt_bias"], inp["lower_bound"], fwd_fn=oracle.fwd)
+        ret[rank] = "no error"
+    except RuntimeError as e:
+        ret[rank] = str(e)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_bad_shard_length_fails_before_any_collective():
+    ret = mp.Manager().dict()
+    mp.spawn(_bad_shard_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert "multiple of 16" in ret[0]      # rank 0 is not the last shard: rejected
+    assert "another rank" in ret[1]        # the last rank's own shard is fine; it learns of rank 0's verdict
 
 
 def test_fold_is_needed_with_weak_decay():
