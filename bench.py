@@ -75,6 +75,9 @@ def parse():
     ap.add_argument("--seq-parts", type=int, default=1,
                     help="single GPU, B=1: split the sequence into this many pieces that run side by side "
                          "(flashkda_b200.cp.fwd_sequence_parallel; approximate at piece boundaries)")
+    ap.add_argument("--cp-check", action="store_true",
+                    help="context-parallel runs: the last rank also runs the whole sequence alone (exact) and reports "
+                         "how far its shard of out and the final state are from that")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target duration of the CPU baseline sample")
     return ap.parse_args()
 
@@ -194,7 +197,8 @@ def run_reference_arm(a):
     desc = f"1 sequence x T={sample.T} x H={sample.H} of {w.name} (B={w.B}, T={w.T}, H={w.H})"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
-        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": a.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if (a.scaling == "strong" and w.seq_lens is None and w.B % max(1, a.gpus) == 0) else "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config_dict(w, a.algo or flashkda_b200.default_algo()),
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
@@ -227,20 +231,22 @@ def run_ours(a):
     # One long sequence (cfg5) on several GPUs: context parallel, every rank holds T / N tokens
     # (strong scaling, one all-gather of the per-shard state maps per step).
     cp_mode = w.name == "cfg5" and world > 1
-    strong = cp_mode   # whether the ranks share ONE problem (value = its tokens / time) or each run their own
+    # whether the ranks share ONE problem (value = its tokens / time) or each run their own copy
+    strong = cp_mode or (a.scaling == "strong" and w.seq_lens is None and w.B % world == 0)
     if cp_mode:
         from flashkda_b200 import cp
         from flashkda_b200.synth import Workload
         w_local = Workload("cfg5-shard", 1, w.T // world // 16 * 16, w.H, lower_bound=w.lower_bound,
                            state_out=w.state_out)
         inp = make_inputs(w_local, device=dev, seed=rank)
+        head = make_inputs(Workload("cfg5-params", 1, 16, w.H), device=dev, seed=w.seed)   # one set of per-head parameters
+        inp["A_log"], inp["dt_bias"] = head["A_log"], head["dt_bias"]
     elif world > 1 and a.scaling == "strong" and w.seq_lens is None and w.B % world == 0:
         # one fixed problem: this rank takes B / N of its sequences (contiguous), no collective on the data path
         from flashkda_b200.synth import Workload, make_inputs_partition
         per = w.B // world
         w_local = Workload(w.name, per, w.T, w.H, lower_bound=w.lower_bound, state_in=w.state_in, state_out=w.state_out)
         inp = make_inputs_partition(w, rank * per, per, device=dev)
-        strong = True
     elif world == 1 and w.seq_lens is None:
         from flashkda_b200.synth import make_inputs_partition
         w_local = w
@@ -352,6 +358,30 @@ def run_ours(a):
         kernel_name = "whole step (several forward calls: sequence split / context parallel)"
         kernel_ms = ms_step
 
+    # ---- context parallel: distance from the exact single-GPU run (optional) ----
+    cp_check = None
+    if cp_mode and a.cp_check:
+        res = [None]
+        if rank == world - 1:
+            full = [make_inputs(w_local, device=dev, seed=r) for r in range(world)]
+            cat = lambda key: torch.cat([f[key] for f in full], dim=1)
+            q, k, v, g, beta = (cat(key) for key in ("q", "k", "v", "g", "beta"))
+            del full
+            out_x = torch.empty_like(v)
+            hT_x = torch.zeros_like(inp["final_state"])
+            flashkda_b200.fwd(q, k, v, g, beta, inp["scale"], out_x, A_log=inp["A_log"], dt_bias=inp["dt_bias"],
+                              lower_bound=inp["lower_bound"], final_state=hT_x)
+            torch.cuda.synchronize(dev)
+            mine = out_x[:, rank * w_local.T:(rank + 1) * w_local.T].float()
+            err = lambda ref, x: ((ref - x).square().mean().sqrt() / (ref.square().mean().sqrt() + 1e-8)).item()
+            res[0] = {"state_ratio": err(hT_x.float(), inp["final_state"].float()),
+                      "out_ratio_last_shard": err(mine, inp["out"].float()),
+                      "out_max_abs_last_shard": (mine - inp["out"].float()).abs().max().item(),
+                      "against": "one exact forward of all %d tokens on the last rank" % (w_local.T * world)}
+            del q, k, v, g, beta, out_x
+        dist.broadcast_object_list(res, src=world - 1)
+        cp_check = res[0]
+
     # ---- end to end through the host-buffer API ----
     e2e = None
     if not a.no_e2e and not cp_mode:
@@ -424,6 +454,10 @@ def run_ours(a):
                      "slowest_kernel": kernel_name, "kernels": per_kernel},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * a.steps, "clocks": clocks,
     }
+    if cp_mode:
+        line["config"]["pieces_per_gpu"] = max(1, a.seq_parts)
+        if cp_check is not None:
+            line["cp_check"] = cp_check
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

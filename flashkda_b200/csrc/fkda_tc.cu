@@ -14,8 +14,7 @@
 //   * the other element-wise steps (bf16 roundings, beta) by the same threads (thread v = TMEM lane v of
 //     D1/D2/D3), reading accumulators with tcgen05.ld.
 // The kernels live in their own files and share the helpers below: fkda_tc_ts.cuh (three chains per CTA: the
-// default for more chains than SMs), fkda_tc_wide.cuh (one chain per CTA, for no more chains than SMs) and
-// fkda_short.cuh (sequences of at most one chunk).
+// default for more chains than SMs) and fkda_tc_wide.cuh (one chain per CTA, for no more chains than SMs).
 //
 // Numerics: steps B1-B7 of the reference's contract (tests/torch_ref.py:231-251; the reference's own
 // recurrence is csrc/smxx/fwd_kernel2.cuh:434-742, built on mma.sync with register transposes).

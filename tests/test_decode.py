@@ -39,7 +39,7 @@ def test_decode_kernel_matches_general_path():
     inp = make_inputs(w, seed=7)
     out_d, hT_d = run_gpu(inp, "tc")
     assert flashkda_b200.last_launch_count() == 1
-    out_g, hT_g = run_gpu(inp, "tc", flags=_lib.FLAG_NO_DECODE | _lib.FLAG_NO_SHORT)
+    out_g, hT_g = run_gpu(inp, "tc", flags=_lib.FLAG_NO_DECODE)
     assert flashkda_b200.last_launch_count() == 2  # prepare + recurrence
     out_c, hT_c = run_gpu(inp, "twopass")
     mism = (out_d != out_g).float().mean().item()
