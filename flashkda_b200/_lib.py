@@ -9,7 +9,7 @@ FKDA_STATE_BF16, FKDA_STATE_FP32 = 0, 1
 ALGO_AUTO, ALGO_TWOPASS, ALGO_TC = 0, 1, 2
 PHASE_PREPARE, PHASE_RECURRENCE = 1, 2
 # fkda_fwd_params.flags (tests and tuning; 0 in production)
-FLAG_NO_DECODE, FLAG_NO_WIDE, FLAG_NO_SLABS, FLAG_TEST_DROP_PUSH = 1, 2, 4, 16
+FLAG_NO_DECODE, FLAG_NO_WIDE, FLAG_NO_SLABS, FLAG_NO_SHORT, FLAG_TEST_DROP_PUSH = 1, 2, 4, 8, 16
 
 
 def flags_seg_chunks(n: int) -> int:

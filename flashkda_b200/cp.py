@@ -108,7 +108,7 @@ def _check_shard_arguments(q, k, v, g, beta, out, initial_state, final_state, ra
 
 
 def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bound, initial_state=None,
-                         final_state=None, group=None, fwd_fn: Callable = None, parts: int = 1):
+                         final_state=None, group=None, fwd_fn: Callable = None, parts: int = 1, validate: bool = True):
     """Forward over one sequence sharded across the ranks of ``group`` (contiguous shards in rank
     order, B = 1, every shard but the last a multiple of 16 tokens).  ``initial_state`` (bf16 or fp32) is
     used by rank 0; ``final_state`` (optional, any rank, either dtype) receives the state after the last
@@ -117,10 +117,15 @@ def fwd_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower_bou
     With the device operator (``fwd_fn`` left None) every rank prepares its chunk records ONCE and runs its
     recurrences over them (the maps ``N`` and ``M``, then the real pass), and ``parts`` > 1 additionally
     splits the rank's shard into that many pieces that run side by side (``SequenceSplit``).  A caller-given
-    ``fwd_fn`` (tests: the CPU oracle) is called with the reference signature only."""
+    ``fwd_fn`` (tests: the CPU oracle) is called with the reference signature only.
+
+    ``validate`` (default on): the ranks agree on the validity of their arguments before the data-path collectives
+    (one 4-byte all-reduce whose result the host reads, i.e. one host synchronisation per call); a caller that has
+    validated its shards once and calls in a hot loop may turn it off."""
     import torch.distributed as dist
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    _check_shard_arguments(q, k, v, g, beta, out, initial_state, final_state, rank, world, group)
+    if validate:
+        _check_shard_arguments(q, k, v, g, beta, out, initial_state, final_state, rank, world, group)
     H, dev = q.shape[2], q.device
     payload = torch.zeros(2, 1, H, D, D, dtype=torch.float32, device=dev)
     S0 = None if initial_state is None else initial_state.to(torch.float32)   # maps and folds are fp32

@@ -97,6 +97,8 @@ int fkda_fwd(const fkda_fwd_params* p, void* stream_v) {
     int rc;
     if (algo == FKDA_ALGO_TC && fkda::decode_eligible(*p) && !(p->flags & FKDA_FLAG_NO_DECODE) && p->chunk_states == nullptr)
         rc = fkda::launch_decode(*p, stream, &launches);  // one token per sequence: state read-modify-write
+    else if (algo == FKDA_ALGO_TC && fkda::short_eligible(*p) && !(p->flags & FKDA_FLAG_NO_SHORT))
+        rc = fkda::launch_short(*p, stream, &launches);   // at most one chunk per sequence: one fused kernel
     else if (algo == FKDA_ALGO_TC)
         rc = fkda::launch_tc(*p, stream, &launches);
     else

@@ -64,6 +64,9 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
 // Decode step (fixed batch, T == 1): one read-modify-write kernel over the states, no workspace records.
 bool decode_eligible(const fkda_fwd_params& p);
 int launch_decode(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
+// Short sequences (fixed batch, 2 <= T <= 16): one fused kernel per (sequence, head), no workspace records.
+bool short_eligible(const fkda_fwd_params& p);
+int launch_short(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
 
 // Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
 // workspace carving).

@@ -8,6 +8,8 @@
 // a persistent kernel.  Numerics: tests/torch_ref.py:153-229 of the reference.
 #pragma once
 
+#include <stddef.h>
+
 #include "fkda_common.cuh"
 #include "fkda_internal.h"
 #include "fkda_sm100.cuh"
@@ -26,6 +28,9 @@ struct alignas(16) PrepWarpSmem {
     float beta_act[kChunk];
 };
 static_assert(16 * kPwKiLbo <= kTcKrBytes, "the ki tile fits the KR buffer");
+static_assert(offsetof(PrepWarpSmem, b1) == kTcB1 && offsetof(PrepWarpSmem, kikr) == kTcKr &&
+              offsetof(PrepWarpSmem, beta_act) == kTcInv && sizeof(float) * kChunk <= 512,
+              "the per-warp tiles coincide with the B1 and KR parts of a record (kRecordInSmem)");
 
 // Where chunk `tile` of the (possibly ragged) batch lives: first token and number of valid rows.
 // Returns false for a tile index past the last chunk (ragged upper bound).
@@ -128,7 +133,10 @@ __device__ __forceinline__ void prep_prefetch(const TwoPassArgs& a, int64_t t0, 
 
 // One warp, one (chunk, head).  `ws` is the record to fill; kTc selects its layout (see fkda_common.cuh).
 // `pf` holds the prefetched head of this chunk and leaves holding that of the next unit (if `next_valid`).
-template <bool kTc>
+// kRecordInSmem (tensor-core layout only): `ws` and `sm` are the SAME 14 656 bytes of shared memory; the record
+// stays there for a consumer in the same CTA (B1 and KR are built in place, nothing is copied; the sigmoid(beta)
+// scratch at the start of the INV tile is consumed before the inverse is written).
+template <bool kTc, bool kRecordInSmem = false>
 __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t t0, int len, int h, uint8_t* ws,
                                                    PrepWarpSmem& sm, int lane, PrepPrefetch& pf, bool next_valid,
                                                    int64_t next_t0, int next_len, int next_h) {
@@ -286,7 +294,7 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
                 *reinterpret_cast<uint2*>(ws + kWsKr + (r * kD + c4) * 2) = kr[r];
         }
     }
-    if constexpr (kTc) {  // ship [kd; qd] and kr: two bulk copies shared memory -> workspace record
+    if constexpr (kTc && !kRecordInSmem) {  // ship [kd; qd] and kr: two bulk copies shared memory -> workspace record
         sm100::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -296,7 +304,7 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
         }
     }
     neumann_inverse_warp<kTc>(lfrag, ws + (kTc ? kTcInv : kWsInv), lane);
-    if constexpr (kTc) {  // the tiles are rewritten by the next chunk: the copies must have read them
+    if constexpr (kTc && !kRecordInSmem) {  // the tiles are rewritten by the next chunk: the copies must have read them
         if (lane == 0) sm100::bulk_wait_group_read<0>();
     }
     __syncwarp();

@@ -1,0 +1,241 @@
+// Short sequences: a fixed batch whose sequences hold 2 .. 16 tokens each (ONE chunk per sequence), the step
+// between a decode step (one token, fkda_decode.cu) and prefill -- e.g. the verification pass of speculative
+// decoding.  Such a batch is bound by HBM traffic on the [128,128] states (read once, written once), so the whole
+// forward of a (sequence, head) chain runs in ONE kernel with nothing staged in HBM: no chunk records, no second
+// launch, 256 bytes of workspace.
+//
+// One 128-thread CTA per FOUR chains, three CTAs per SM:
+//   * first every warp runs the prepare stage of one of the four chunks (the same warp-per-chunk routine as the
+//     prefill path), record left in shared memory: the prepare stage is a long serial instruction stream, so four
+//     of them run side by side instead of three warps waiting for one;
+//   * after one block barrier the four chains are walked one after the other by all four warps: every warp loads
+//     its 32 state rows straight into mma.sync A-fragment registers (thread g = lane / 4, tq = lane % 4 of warp w
+//     holds rows 32 w + 16 mt + {g, g + 8}, columns 16 j + {2tq, 2tq+1, 2tq+8, 2tq+9} for the row tiles mt = 0, 1 and
+//     the K steps j = 0 .. 7) and runs the chunk step on mma.sync, state in registers throughout:
+//       D1[V,32] = S . [kd; qd]^T   (8 K steps in order: the reference's accumulation order)
+//       u' = (v (-) bf(u0)) (*) bf(beta),  U = bf(u' INV^T),  out = bf(o0) (+) bf(U Mqk^T)
+//       DST[V,K] = U^T . kr,  S[v,k] = bf(fma(S[v,k], E_tot[k], DST[v,k]))  (accumulator and A fragments of a
+//       16 x 16 block hold the same elements, so the update runs fragment on fragment)
+//     and store their rows of the final state from the fragments.
+// Numerics and results: those of the chunked kernels on the same inputs (tests/torch_ref.py:153-251 of the
+// reference; the reference itself runs such batches through its two general kernels,
+// csrc/smxx/fwd_kernel1.cuh / fwd_kernel2.cuh).
+#include "fkda_common.cuh"
+#include "fkda_internal.h"
+#include "fkda_prepare_warp.cuh"
+
+namespace fkda {
+
+// B operand fragments of mma.sync m16n8k16 for n-tile rows r = 8 nt + g of a K-major [rows, K] tile in the record's
+// B1 layout (byte = (k/8)*528 + (r/8)*128 + (r%8)*16 + (k%8)*2): b0 = (k 16j + 2tq, +1), b1 = (k 16j + 8 + 2tq, +1)
+__device__ __forceinline__ void short_b1_frag(const uint8_t* b1, int r, int j, int tq, uint32_t& b0, uint32_t& b1r) {
+    const uint8_t* p = b1 + (2 * j) * kTcB1Lbo + (r >> 3) * 128 + (r & 7) * 16 + tq * 4;
+    b0 = *reinterpret_cast<const uint32_t*>(p);
+    b1r = *reinterpret_cast<const uint32_t*>(p + kTcB1Lbo);
+}
+// Four 8x8 b16 matrices, transposed on the way: lane 8m + r gives the address of row r (16 bytes) of matrix m; thread
+// (g, tq) receives elements (rows 2tq, 2tq+1; column g) of each, i.e. mma.sync B fragments of row-major [K, N] tiles.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* row_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+constexpr int kShortChainsPerCta = 4;
+constexpr int kShortSmemBytes = kShortChainsPerCta * kTcRecord + 16;
+
+__global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ TwoPassArgs a) {
+    extern __shared__ uint8_t short_smem[];
+    uint8_t* recs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(short_smem) + 15) & ~(uintptr_t)15);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const int64_t n_chains = a.N * a.H;
+    const int64_t chain0 = (int64_t)blockIdx.x * kShortChainsPerCta;
+    const int len = (int)a.T;                 // 2 .. 16 tokens, one chunk
+    const int row0 = warp * 32 + g;           // my rows: row0 + 16 mt + 8 hi
+
+    // ---- the operands of the four chunks: warp w runs the prepare stage of chain chain0 + w, record left in
+    //      shared memory (layout of fkda_common.cuh) ----
+    if (chain0 + warp < n_chains) {
+        const int64_t n = (chain0 + warp) / a.H;
+        const int h = (int)(chain0 + warp - n * a.H);
+        uint8_t* rec = recs + warp * kTcRecord;
+        PrepPrefetch pf;
+        prep_prefetch(a, n * a.T, len, h, lane, pf);
+        prepare_chunk_warp<true, true>(a, n * a.T, len, h, rec, *reinterpret_cast<PrepWarpSmem*>(rec), lane, pf, false, 0, 0, 0);
+    }
+    __syncthreads();   // the four records are complete
+
+#pragma unroll 1
+    for (int ci = 0; ci < kShortChainsPerCta; ++ci) {
+    const int64_t chain = chain0 + ci;
+    if (chain >= n_chains) break;
+    const int64_t n = chain / a.H;
+    const int h = (int)(chain - n * a.H);
+    const int64_t t0 = n * a.T;
+    const uint8_t* rec = recs + ci * kTcRecord;
+
+    // ---- state rows into A-fragment registers: sreg[mt][j][e], e = {row g: cols 2tq | row g+8 | row g: cols 2tq+8 | row g+8} ----
+    uint32_t sreg[2][8][4];
+    const int64_t st_chain = chain * (int64_t)(kD * kD);
+    if (a.initial_state != nullptr) {
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int64_t off = st_chain + (int64_t)(row0 + 16 * mt + 8 * (e & 1)) * kD + 16 * j + 8 * (e >> 1) + 2 * tq;
+                    if (a.state_fp32) {
+                        const float2 x = __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(a.initial_state) + off));
+                        sreg[mt][j][e] = pack_bf2(x.x, x.y);
+                    } else {
+                        sreg[mt][j][e] = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned short*>(a.initial_state) + off));
+                    }
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sreg[mt][j][e] = 0u;
+    }
+    // value tile in A-fragment layout (zero past the sequence end), straight from global memory
+    uint32_t vfr[2][4];
+    {
+        const unsigned short* vp = reinterpret_cast<const unsigned short*>(a.v) + t0 * a.token_stride + (int64_t)h * kD;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = row0 + 16 * mt + 8 * (e & 1), tok = 2 * tq + 8 * (e >> 1);
+                const uint32_t lo = tok < len ? vp[(int64_t)tok * a.token_stride + row] : 0u;
+                const uint32_t hi = tok + 1 < len ? vp[(int64_t)(tok + 1) * a.token_stride + row] : 0u;
+                vfr[mt][e] = lo | (hi << 16);
+            }
+        }
+    }
+
+    // ---- D1[V,32] = S . [kd; qd]^T: rows 0-15 of B1 are kd (-> u0), rows 16-31 qd (-> o0) ----
+    float d1[2][4][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d1[mt][nt][i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            uint32_t b0, b1;
+            short_b1_frag(rec + kTcB1, 8 * nt + g, j, tq, b0, b1);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+                mma_bf16_f32acc(d1[mt][nt], sreg[mt][j][0], sreg[mt][j][1], sreg[mt][j][2], sreg[mt][j][3], b0, b1);
+        }
+    }
+    // ---- u' = (v (-) bf(u0)) (*) bf(beta);  U = bf(u' INV^T);  out = bf(o0) (+) bf(U Mqk^T) ----
+    const uint32_t* beta32 = reinterpret_cast<const uint32_t*>(rec + kTcBeta);
+    const uint32_t bp0 = beta32[tq], bp1 = beta32[tq + 4];
+    uint32_t invb[2][2], mqkb[2][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+        invb[nt][0] = *reinterpret_cast<const uint32_t*>(rec + kTcInv + tc_sq_off(8 * nt + g, 2 * tq));
+        invb[nt][1] = *reinterpret_cast<const uint32_t*>(rec + kTcInv + tc_sq_off(8 * nt + g, 2 * tq + 8));
+        mqkb[nt][0] = *reinterpret_cast<const uint32_t*>(rec + kTcMqk + tc_sq_off(8 * nt + g, 2 * tq));
+        mqkb[nt][1] = *reinterpret_cast<const uint32_t*>(rec + kTcMqk + tc_sq_off(8 * nt + g, 2 * tq + 8));
+    }
+    uint32_t ufr[2][4];
+    unsigned short* og = reinterpret_cast<unsigned short*>(a.out) + t0 * a.token_stride + (int64_t)h * kD;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+        uint32_t up[4];   // accumulator tiles nt = 0, 1 of D1 are u0 for tokens 0-7, 8-15: {c0,c1 | c2,c3} = {row g | row g+8}
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const uint32_t u0 = pack_bf2(d1[mt][e >> 1][2 * (e & 1)], d1[mt][e >> 1][2 * (e & 1) + 1]);
+            up[e] = bf2_mul(bf2_sub(vfr[mt][e], u0), (e >> 1) ? bp1 : bp0);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_bf16_f32acc(c, up[0], up[1], up[2], up[3], invb[nt][0], invb[nt][1]);
+            ufr[mt][2 * nt] = pack_bf2(c[0], c[1]);
+            ufr[mt][2 * nt + 1] = pack_bf2(c[2], c[3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_bf16_f32acc(c, ufr[mt][0], ufr[mt][1], ufr[mt][2], ufr[mt][3], mqkb[nt][0], mqkb[nt][1]);
+#pragma unroll
+            for (int hi = 0; hi < 2; ++hi) {
+                const uint32_t o = bf2_add(pack_bf2(d1[mt][2 + nt][2 * hi], d1[mt][2 + nt][2 * hi + 1]), pack_bf2(c[2 * hi], c[2 * hi + 1]));
+                const int row = row0 + 16 * mt + 8 * hi, tok = 8 * nt + 2 * tq;
+                if (tok < len) og[(int64_t)tok * a.token_stride + row] = (unsigned short)(o & 0xffffu);
+                if (tok + 1 < len) og[(int64_t)(tok + 1) * a.token_stride + row] = (unsigned short)(o >> 16);
+            }
+        }
+    }
+    if (a.final_state == nullptr) continue;
+
+    // ---- DST[V,K] = U^T . kr and S[v,k] = bf(fma(S[v,k], E_tot[k], DST[v,k])), 16 state columns (K step j) at a time;
+    //      the refreshed fragments go straight to the final state ----
+    const float* et = reinterpret_cast<const float*>(rec + kTcEt);
+    // KR tile: kr[token i][column k] at (i/8)*2304 + (k/8)*144 + (i%8)*16 + (k%8)*2: 8x8 blocks with tokens as rows.
+    // ldmatrix lane 8m + r: matrix m = (token group m & 1, column block 2j + (m >> 1)), row r = token
+    const uint8_t* kr_row = rec + kTcKr + ((lane >> 3) & 1) * kTcKrLbo + (lane >> 4) * kTcKrSbo + (lane & 7) * 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        uint32_t b00, b01, b10, b11;   // column block 2j: tokens 0-7, 8-15; column block 2j+1: tokens 0-7, 8-15
+        ldmatrix_x4_trans(b00, b01, b10, b11, kr_row + (2 * j) * kTcKrSbo);
+        const float2 e0 = *reinterpret_cast<const float2*>(et + 16 * j + 2 * tq);        // E_tot of columns 16j + 2tq, +1
+        const float2 e1 = *reinterpret_cast<const float2*>(et + 16 * j + 8 + 2 * tq);    // 16j + 8 + 2tq, +1
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_bf16_f32acc(c0, ufr[mt][0], ufr[mt][1], ufr[mt][2], ufr[mt][3], b00, b01);   // columns 16j + 0..7
+            mma_bf16_f32acc(c1, ufr[mt][0], ufr[mt][1], ufr[mt][2], ufr[mt][3], b10, b11);   // columns 16j + 8..15
+            const uint32_t s0 = sreg[mt][j][0], s1 = sreg[mt][j][1], s2 = sreg[mt][j][2], s3 = sreg[mt][j][3];
+            const uint32_t y0 = pack_bf2(__fmaf_rn(bf_lo(s0), e0.x, c0[0]), __fmaf_rn(bf_hi(s0), e0.y, c0[1]));   // row g
+            const uint32_t y1 = pack_bf2(__fmaf_rn(bf_lo(s1), e0.x, c0[2]), __fmaf_rn(bf_hi(s1), e0.y, c0[3]));   // row g+8
+            const uint32_t y2 = pack_bf2(__fmaf_rn(bf_lo(s2), e1.x, c1[0]), __fmaf_rn(bf_hi(s2), e1.y, c1[1]));
+            const uint32_t y3 = pack_bf2(__fmaf_rn(bf_lo(s3), e1.x, c1[2]), __fmaf_rn(bf_hi(s3), e1.y, c1[3]));
+            const uint32_t y[4] = {y0, y1, y2, y3};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int64_t off = st_chain + (int64_t)(row0 + 16 * mt + 8 * (e & 1)) * kD + 16 * j + 8 * (e >> 1) + 2 * tq;
+                if (a.state_fp32)
+                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.final_state) + off) = make_float2(bf_lo(y[e]), bf_hi(y[e]));
+                else
+                    *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(a.final_state) + off) = y[e];
+            }
+        }
+    }
+    }   // chains of this CTA
+}
+
+bool short_eligible(const fkda_fwd_params& p) {
+    return p.cu_seqlens == nullptr && p.T >= 2 && p.T <= kChunk && p.chunk_states == nullptr &&
+           (p.phase_mask == 0 || p.phase_mask == (FKDA_PHASE_PREPARE | FKDA_PHASE_RECURRENCE));
+}
+
+int launch_short(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
+    TwoPassArgs a;
+    fill_args(p, &a);
+    if (cudaMemsetAsync(p.workspace, 0, 16, stream) != cudaSuccess) return FKDA_ERR_LAUNCH;  // header: device status
+    const int64_t chains = p.N * p.H;
+    if (chains > 0x7fffffff) return FKDA_ERR_BAD_SHAPE;
+    if (cudaFuncSetAttribute(short_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kShortSmemBytes) != cudaSuccess)
+        return FKDA_ERR_LAUNCH;
+    const int64_t ctas = (chains + kShortChainsPerCta - 1) / kShortChainsPerCta;
+    short_kernel<<<(unsigned)ctas, 128, kShortSmemBytes, stream>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return FKDA_ERR_LAUNCH;
+    *n_launches = 1;
+    return FKDA_OK;
+}
+
+}  // namespace fkda

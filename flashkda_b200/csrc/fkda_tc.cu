@@ -296,6 +296,7 @@ static TcCarve tc_carve(const fkda_fwd_params& p, int sms) {
 }
 size_t tc_workspace_bytes_for(const fkda_fwd_params& p) {
     if (decode_eligible(p) && !(p.flags & FKDA_FLAG_NO_DECODE) && p.chunk_states == nullptr) return kWsHeaderBytes;  // status word only
+    if (short_eligible(p) && !(p.flags & FKDA_FLAG_NO_SHORT)) return kWsHeaderBytes;
     const TcCarve c = tc_carve(p, device_sm_count());
     return kWsHeaderBytes + ws_prefix_bytes(p.N) + c.slots + c.states + c.records;
 }

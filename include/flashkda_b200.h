@@ -48,7 +48,8 @@ enum {
     FKDA_ALGO_AUTO = 0,
     FKDA_ALGO_TWOPASS = 1, /* prepare kernel -> HBM workspace -> recurrence kernel (CUDA cores) */
     FKDA_ALGO_TC = 2       /* prepare kernel -> HBM workspace -> persistent tcgen05/TMEM recurrence; a fixed batch
-                              with T == 1 (decode step) runs one state read-modify-write kernel instead */
+                              with T == 1 (decode step) runs one state read-modify-write kernel instead, one with
+                              2 <= T <= 16 one fused kernel per (sequence, head) */
 };
 
 /*
@@ -101,6 +102,7 @@ enum {
     FKDA_FLAG_NO_DECODE = 1,       /* run a T == 1 batch through the chunked kernels instead of the decode kernel */
     FKDA_FLAG_NO_WIDE = 2,         /* never pick the one-chain-per-CTA recurrence */
     FKDA_FLAG_NO_SLABS = 4,        /* no slab pipeline (prepare of the next slab beside the recurrence) */
+    FKDA_FLAG_NO_SHORT = 8,        /* run a batch of 2..16-token sequences through the general kernels */
     FKDA_FLAG_TEST_DROP_PUSH = 16  /* TEST ONLY: finished segments do not queue their follow-up, so that the
                                       work queue starves and its bounded waits give up */
 };

@@ -217,6 +217,21 @@ def test_out_rows_past_sequence_end_untouched_and_inputs_unmodified(algo):
     assert torch.equal(out2, d["out"][:, :25])
 
 
+@pytest.mark.parametrize("state_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,H", [(2, 3), (40, 16)])
+def test_empty_batch_passes_the_state_through(B, H, state_dtype, algo):
+    """T = 0: nothing to compute; final_state receives the bf16-rounded initial state (what a zero-length sequence
+    does inside a ragged batch, reference csrc/smxx/fwd_kernel2.cuh:314), on every recurrence kernel."""
+    e = lambda *shape: torch.zeros(*shape, dtype=torch.bfloat16, device="cuda")
+    h0 = (torch.randn(B, H, 128, 128, generator=torch.Generator().manual_seed(1)) * 0.3).cuda().to(state_dtype)
+    hT = torch.full_like(h0, 5.0)
+    flashkda_b200.fwd(e(B, 0, H, 128), e(B, 0, H, 128), e(B, 0, H, 128), e(B, 0, H, 128), e(B, 0, H), 0.1, e(B, 0, H, 128),
+                      A_log=torch.zeros(H, device="cuda"), dt_bias=torch.zeros(H, 128, device="cuda"), lower_bound=-1.0,
+                      initial_state=h0, final_state=hT, algo=algo)
+    torch.cuda.synchronize()
+    assert torch.equal(hT, h0.to(torch.bfloat16).to(state_dtype))
+
+
 def test_host_argument_errors_on_gpu():
     inp = to_device(make_inputs(Workload("e", 1, 32, 2)), "cuda")
     args = lambda **kw: dict(dict(A_log=inp["A_log"], dt_bias=inp["dt_bias"], lower_bound=-5.0), **kw)
