@@ -340,10 +340,11 @@ def run_ours(a):
     kernel_times = {}
     n_phase = 3
     barrier()
-    decode = w_local.T == 1 and inp.get("cu_seqlens") is None and algo != "twopass"
-    if decode and not cp_mode and a.seq_parts == 1:
-        # one token per sequence: the library runs its single decode kernel (no phases to time apart)
-        kernel_name, kernel_ms = "fkda::decode_kernel", ms_step
+    decode = w_local.T == 1 and inp.get("cu_seqlens") is None and algo != "twopass" and not (a.flags & 1)
+    short = 2 <= w_local.T <= 16 and inp.get("cu_seqlens") is None and algo != "twopass" and not (a.flags & 8)
+    if (decode or short) and not cp_mode and a.seq_parts == 1:
+        # at most one chunk per sequence: the library runs ONE kernel (no phases to time apart)
+        kernel_name, kernel_ms = ("fkda::decode_kernel" if decode else "fkda::short_kernel"), ms_step
         kernel_times[kernel_name] = ms_step
     elif not cp_mode and a.seq_parts == 1:
         step()
@@ -417,7 +418,7 @@ def run_ours(a):
     state_bytes = alg_bytes - th * 1282 if not cp_mode else 0
     rec = {"twopass": 13824}.get(algo, 14656)
     own = {"fkda::prepare_warp_kernel": th * 770 + units * rec,
-           "fkda::decode_kernel": alg_bytes}
+           "fkda::decode_kernel": alg_bytes, "fkda::short_kernel": alg_bytes}
     for n in names[1:]:
         own[n] = units * rec + th * 512 + state_bytes
     tdb = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))) \

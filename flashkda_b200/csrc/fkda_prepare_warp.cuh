@@ -172,6 +172,20 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
     for (int rr = 0; rr < kPf; ++rr) {
         const int r = rb + rr;
         const bool valid = r < len;
+        if (!valid) {
+            // a row past the sequence end (warp-uniform): q = k = 0 and no gate contribution, so its rows of the
+            // tiles are zeros (qd keeps the sign that the multiplication by bf(scale) gives a zero)
+            const uint32_t qz = bf2_mul(0u, sc2);
+            const int off = tc_b1_off(r, lane >> 1) + (lane & 1) * 8;
+            *reinterpret_cast<uint2*>(sm.b1 + off) = make_uint2(0u, 0u);
+            *reinterpret_cast<uint2*>(sm.b1 + off + 2 * 128) = make_uint2(qz, qz);
+            *reinterpret_cast<uint2*>(sm.kikr + (lane >> 1) * kPwKiLbo + (r >> 3) * 128 + (r & 7) * 16 + (lane & 1) * 8) = make_uint2(0u, 0u);
+            if constexpr (!kTc) {
+                *reinterpret_cast<uint2*>(ws + kWsKd + (r * kD + c4) * 2) = make_uint2(0u, 0u);
+                *reinterpret_cast<uint2*>(ws + kWsQd + (r * kD + c4) * 2) = make_uint2(qz, qz);
+            }
+            continue;
+        }
         const uint2 qraw = ring_q[rr], kraw = ring_k[rr], graw = ring_g[rr];
         if (r + kPf < kChunk) fetch(r + kPf, rr);
         const float qv[4] = {bf_lo(qraw.x), bf_hi(qraw.x), bf_lo(qraw.y), bf_hi(qraw.y)};
