@@ -23,6 +23,9 @@ struct TwoPassArgs {
     uint8_t* workspace;    // [H][total_tiles] per-chunk records
     int32_t* queue;        // header word 0: tail / queue ticket counter of the persistent recurrence (zeroed per call)
     int32_t* status;       // header word 1: device status, 0 ok, else the code of a bounded wait that gave up
+    int32_t* short_flag;   // header word 8, or null: written by the prefix kernel of a ragged batch, 1 when no sequence is
+                           // longer than one chunk; the fused short-sequence kernel then serves the call and the general
+                           // kernels, enqueued behind it, return at once (0: the other way round)
                            // (header words 2, 3: push counter and finished-chain counter of the segment queue;
                            //  words 4..6: claim counters of the three layers of first segments)
     int32_t* qslots;       // segment queue: slot i receives the i-th pushed item (-1 = not yet pushed)
@@ -67,12 +70,16 @@ int launch_decode(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches
 // Short sequences (fixed batch, 2 <= T <= 16): one fused kernel per (sequence, head), no workspace records.
 bool short_eligible(const fkda_fwd_params& p);
 int launch_short(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches);
+// Ragged batches: whether the call MAY consist of sequences of at most one chunk each (the host knows only the totals;
+// the prefix kernel decides on the device), and the launch of the fused kernel behind that decision.
+bool short_ragged_candidate(const fkda_fwd_params& p);
+int launch_short_ragged(const TwoPassArgs& a, cudaStream_t stream);
 
 // Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
 // workspace carving).
 void fill_args(const fkda_fwd_params& p, TwoPassArgs* a);
 void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
-                        int cs_tokens, cudaStream_t stream);
+                        int cs_tokens, int32_t* short_flag, cudaStream_t stream);
 // First state-export slot of sequence n.
 __device__ __forceinline__ int64_t cs_first_slot(const TwoPassArgs& a, int64_t n) {
     if (a.cu_seqlens != nullptr) return a.cs_prefix[n];

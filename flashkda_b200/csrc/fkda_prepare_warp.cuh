@@ -329,6 +329,8 @@ __device__ __forceinline__ void prepare_chunk_warp(const TwoPassArgs& a, int64_t
 constexpr int kPwWarpsPerCta = 16;
 template <bool kTc>
 __global__ void __launch_bounds__(kPwWarpsPerCta * 32, 1) prepare_warp_kernel(const __grid_constant__ TwoPassArgs a) {
+    // (a ragged batch that the fused short-sequence kernel has served: nothing to do)
+    if (a.short_flag != nullptr && *a.short_flag != 0) return;
     extern __shared__ __align__(16) uint8_t pw_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     PrepWarpSmem& sm = reinterpret_cast<PrepWarpSmem*>(pw_smem)[warp];

@@ -50,10 +50,22 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
     uint8_t* recs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(short_smem) + 15) & ~(uintptr_t)15);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tq = lane & 3;
+    // a ragged batch: the prefix kernel found a sequence longer than one chunk, the general kernels serve the call
+    if (a.short_flag != nullptr && *a.short_flag == 0) return;
     const int64_t n_chains = a.N * a.H;
     const int64_t chain0 = (int64_t)blockIdx.x * kShortChainsPerCta;
-    const int len = (int)a.T;                 // 2 .. 16 tokens, one chunk
     const int row0 = warp * 32 + g;           // my rows: row0 + 16 mt + 8 hi
+    // first token and length (0 .. 16 tokens: at most one chunk) of sequence n
+    auto locate = [&](int64_t n, int64_t* t0, int* len) {
+        if (a.cu_seqlens != nullptr) {
+            const int64_t b = a.cu_seqlens[n], e = a.cu_seqlens[n + 1];
+            *t0 = b;
+            *len = e > b ? (int)(e - b) : 0;
+        } else {
+            *t0 = n * a.T;
+            *len = (int)a.T;
+        }
+    };
 
     // ---- the operands of the four chunks: warp w runs the prepare stage of chain chain0 + w, record left in
     //      shared memory (layout of fkda_common.cuh) ----
@@ -61,9 +73,14 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
         const int64_t n = (chain0 + warp) / a.H;
         const int h = (int)(chain0 + warp - n * a.H);
         uint8_t* rec = recs + warp * kTcRecord;
-        PrepPrefetch pf;
-        prep_prefetch(a, n * a.T, len, h, lane, pf);
-        prepare_chunk_warp<true, true>(a, n * a.T, len, h, rec, *reinterpret_cast<PrepWarpSmem*>(rec), lane, pf, false, 0, 0, 0);
+        int64_t t0;
+        int len;
+        locate(n, &t0, &len);
+        if (len > 0) {
+            PrepPrefetch pf;
+            prep_prefetch(a, t0, len, h, lane, pf);
+            prepare_chunk_warp<true, true>(a, t0, len, h, rec, *reinterpret_cast<PrepWarpSmem*>(rec), lane, pf, false, 0, 0, 0);
+        }
     }
     __syncthreads();   // the four records are complete
 
@@ -73,7 +90,9 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
     if (chain >= n_chains) break;
     const int64_t n = chain / a.H;
     const int h = (int)(chain - n * a.H);
-    const int64_t t0 = n * a.T;
+    int64_t t0;
+    int len;
+    locate(n, &t0, &len);
     const uint8_t* rec = recs + ci * kTcRecord;
 
     // ---- state rows into A-fragment registers: sreg[mt][j][e], e = {row g: cols 2tq | row g+8 | row g: cols 2tq+8 | row g+8} ----
@@ -103,6 +122,25 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
             for (int j = 0; j < 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) sreg[mt][j][e] = 0u;
+    }
+    auto store_state = [&](int mt, int j, const uint32_t (&y)[4]) {   // fragment (mt, j) of the refreshed state
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int64_t off = st_chain + (int64_t)(row0 + 16 * mt + 8 * (e & 1)) * kD + 16 * j + 8 * (e >> 1) + 2 * tq;
+            if (a.state_fp32)
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.final_state) + off) = make_float2(bf_lo(y[e]), bf_hi(y[e]));
+            else
+                *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(a.final_state) + off) = y[e];
+        }
+    };
+    if (len == 0) {   // an empty sequence of a ragged batch: its state passes through (rounded to bf16, as everywhere)
+        if (a.final_state != nullptr) {
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) store_state(mt, j, sreg[mt][j]);
+        }
+        continue;
     }
     // value tile in A-fragment layout (zero past the sequence end), straight from global memory
     uint32_t vfr[2][4];
@@ -205,14 +243,7 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
             const uint32_t y2 = pack_bf2(__fmaf_rn(bf_lo(s2), e1.x, c1[0]), __fmaf_rn(bf_hi(s2), e1.y, c1[1]));
             const uint32_t y3 = pack_bf2(__fmaf_rn(bf_lo(s3), e1.x, c1[2]), __fmaf_rn(bf_hi(s3), e1.y, c1[3]));
             const uint32_t y[4] = {y0, y1, y2, y3};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int64_t off = st_chain + (int64_t)(row0 + 16 * mt + 8 * (e & 1)) * kD + 16 * j + 8 * (e >> 1) + 2 * tq;
-                if (a.state_fp32)
-                    *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.final_state) + off) = make_float2(bf_lo(y[e]), bf_hi(y[e]));
-                else
-                    *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned short*>(a.final_state) + off) = y[e];
-            }
+            store_state(mt, j, y);
         }
     }
     }   // chains of this CTA
@@ -221,6 +252,23 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
 bool short_eligible(const fkda_fwd_params& p) {
     return p.cu_seqlens == nullptr && p.T >= 2 && p.T <= kChunk && p.chunk_states == nullptr &&
            (p.phase_mask == 0 || p.phase_mask == (FKDA_PHASE_PREPARE | FKDA_PHASE_RECURRENCE));
+}
+
+bool short_ragged_candidate(const fkda_fwd_params& p) {
+    // tokens <= 16 per sequence on average is necessary for "no sequence longer than a chunk"; a handful of chains is
+    // not worth two extra launches
+    return p.cu_seqlens != nullptr && p.N > 0 && p.B * p.T <= kChunk * p.N && p.N * p.H >= 64 &&
+           p.chunk_states == nullptr && (p.phase_mask == 0 || p.phase_mask == (FKDA_PHASE_PREPARE | FKDA_PHASE_RECURRENCE));
+}
+
+int launch_short_ragged(const TwoPassArgs& a, cudaStream_t stream) {
+    const int64_t chains = a.N * a.H;
+    if (chains > 0x7fffffff) return FKDA_ERR_BAD_SHAPE;
+    if (cudaFuncSetAttribute(short_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kShortSmemBytes) != cudaSuccess)
+        return FKDA_ERR_LAUNCH;
+    const int64_t ctas = (chains + kShortChainsPerCta - 1) / kShortChainsPerCta;
+    short_kernel<<<(unsigned)ctas, 128, kShortSmemBytes, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? FKDA_OK : FKDA_ERR_LAUNCH;
 }
 
 int launch_short(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {

@@ -32,6 +32,8 @@ constexpr int kTsSmemBytes = kTcChains * kTsChainBytes + (int)sizeof(TcCtrl) + 1
 
 __global__ void __launch_bounds__(kTcChains * 128, 1)
 recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constant__ TcMaps maps) {
+    // (a ragged batch that the fused short-sequence kernel has served: nothing to do)
+    if (a.short_flag != nullptr && *a.short_flag != 0) return;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
     TcCtrl& ctl = *reinterpret_cast<TcCtrl*>(smem + kTcChains * kTsChainBytes);

@@ -104,6 +104,8 @@ __device__ __forceinline__ void wide_store_state(const uint32_t (&sreg)[32], con
 
 __global__ void __launch_bounds__(kWideThreads, 1)
 recurrence_tc_wide_kernel(const __grid_constant__ TwoPassArgs a, const __grid_constant__ TcMaps maps) {
+    // (a ragged batch that the fused short-sequence kernel has served: nothing to do)
+    if (a.short_flag != nullptr && *a.short_flag != 0) return;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* cs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~(uintptr_t)127);
     TcWideCtrl& ctl = *reinterpret_cast<TcWideCtrl*>(cs + kWideCtrlOff);

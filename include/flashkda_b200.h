@@ -102,7 +102,7 @@ enum {
     FKDA_FLAG_NO_DECODE = 1,       /* run a T == 1 batch through the chunked kernels instead of the decode kernel */
     FKDA_FLAG_NO_WIDE = 2,         /* never pick the one-chain-per-CTA recurrence */
     FKDA_FLAG_NO_SLABS = 4,        /* no slab pipeline (prepare of the next slab beside the recurrence) */
-    FKDA_FLAG_NO_SHORT = 8,        /* run a batch of 2..16-token sequences through the general kernels */
+    FKDA_FLAG_NO_SHORT = 8,        /* run a batch of sequences of at most 16 tokens each through the general kernels */
     FKDA_FLAG_TEST_DROP_PUSH = 16  /* TEST ONLY: finished segments do not queue their follow-up, so that the
                                       work queue starves and its bounded waits give up */
 };

@@ -52,3 +52,78 @@ def test_short_batch_needs_no_records():
                       final_state=d["final_state"], workspace=ws)
     torch.cuda.synchronize()
     assert flashkda_b200.device_status(ws) == 0 and torch.isfinite(d["out"].float()).all()
+
+
+# ---- ragged batches whose sequences all fit one chunk (the device decides: the host sees only the totals) ----
+def _ragged_lens(kind):
+    g = torch.Generator().manual_seed(11)
+    if kind == "1..16":
+        return torch.randint(1, 17, (40,), generator=g).tolist()
+    if kind == "ones":            # a decode step handed over as a ragged batch
+        return [1] * 48
+    if kind == "with_empty":
+        lens = torch.randint(0, 17, (44,), generator=g).tolist()
+        lens[0], lens[5], lens[-1] = 0, 0, 0
+        return lens
+    if kind == "full":
+        return [16] * 36
+    raise KeyError(kind)
+
+
+def _run_ragged(inp, flags=0):
+    """Like run_gpu, with a workspace painted beforehand; returns (out, final_state, untouched record bytes?)."""
+    d = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in inp.items()}
+    n = d["cu_seqlens"].numel() - 1
+    need = flashkda_b200.get_workspace_size(d["q"].shape[1], d["q"].shape[2], n)
+    ws = torch.full((need,), 0xAB, dtype=torch.uint8, device="cuda")
+    flashkda_b200.fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], d["scale"], d["out"], A_log=d["A_log"],
+                      dt_bias=d["dt_bias"], lower_bound=d["lower_bound"], initial_state=d["initial_state"],
+                      final_state=d["final_state"], cu_seqlens=d["cu_seqlens"], workspace=ws, flags=flags)
+    torch.cuda.synchronize()
+    assert flashkda_b200.device_status(ws) == 0
+    records_untouched = bool((ws[16384:] == 0xAB).all().item())   # header, prefix tables and queue sit in front
+    return d["out"].cpu(), None if d["final_state"] is None else d["final_state"].cpu(), records_untouched
+
+
+@pytest.mark.parametrize("kind", ["1..16", "ones", "with_empty", "full"])
+@pytest.mark.parametrize("state_dtype", ["bf16", "fp32"])
+def test_ragged_short_batch_matches_general_path_and_oracle(kind, state_dtype):
+    lens = _ragged_lens(kind)
+    w = Workload("rs", 1, sum(lens), 2, state_in=state_dtype, state_out=state_dtype, lower_bound=-2.0, seq_lens=lens)
+    inp = make_inputs(w, seed=21)
+    out_s, hT_s, untouched = _run_ragged(inp)
+    assert flashkda_b200.last_launch_count() == 4   # prefix, fused kernel, and the two general kernels that return at once
+    assert untouched, "the fused kernel keeps no chunk records"
+    out_g, hT_g, untouched_g = _run_ragged(inp, flags=_lib.FLAG_NO_SHORT)
+    assert flashkda_b200.last_launch_count() == 3 and not untouched_g
+    assert torch.equal(out_s, out_g) and torch.equal(hT_s, hT_g)
+    ref_out, ref_hT = run_oracle(inp)
+    check_against(out_s, hT_s, ref_out, ref_hT)
+    for n, L in enumerate(lens):
+        if L == 0:
+            assert torch.equal(hT_s[n].float(), inp["initial_state"][n].to(torch.bfloat16).float())
+
+
+def test_ragged_batch_with_one_longer_sequence_takes_the_general_kernels():
+    lens = [3] * 47 + [17]    # 16 tokens per sequence or fewer on average, but not each
+    w = Workload("rl", 1, sum(lens), 2, state_in="fp32", state_out="fp32", lower_bound=-2.0, seq_lens=lens)
+    inp = make_inputs(w, seed=22)
+    out_s, hT_s, untouched = _run_ragged(inp)
+    assert flashkda_b200.last_launch_count() == 4 and not untouched
+    out_g, hT_g, _ = _run_ragged(inp, flags=_lib.FLAG_NO_SHORT)
+    assert torch.equal(out_s, out_g) and torch.equal(hT_s, hT_g)
+    ref_out, ref_hT = run_oracle(inp)
+    check_against(out_s, hT_s, ref_out, ref_hT)
+
+
+def test_ragged_short_batch_without_states_and_many_chains():
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(1, 17, (300,), generator=g).tolist()
+    w = Workload("rm", 1, sum(lens), 8, lower_bound=-1.0, seq_lens=lens)   # 2 400 chains: the segment queue's regime
+    inp = make_inputs(w, seed=23)
+    out_s, _, _ = _run_ragged(inp)   # (the queue slots of this regime are reset by the host either way)
+    assert flashkda_b200.last_launch_count() == 4
+    out_g, _, _ = _run_ragged(inp, flags=_lib.FLAG_NO_SHORT)
+    assert torch.equal(out_s, out_g)
+    ref_out, _ = run_oracle(inp)
+    check_against(out_s, None, ref_out, None)
