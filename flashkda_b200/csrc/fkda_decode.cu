@@ -34,6 +34,9 @@ __device__ __forceinline__ float warp_rows_reduce(float (&x)[32], int lane) {
 }
 
 __global__ void __launch_bounds__(128, 3) decode_kernel(const __grid_constant__ TwoPassArgs a) {
+    // a ragged batch with as many tokens as sequences: mine only if the prefix kernel found one token in each (then
+    // sequence n is token n, as in a fixed batch)
+    if (a.short_flag != nullptr && *a.short_flag != 2) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t chain = blockIdx.x;
     const int64_t n = chain / a.H;          // sequence = token index (T == 1)
@@ -156,6 +159,13 @@ __global__ void __launch_bounds__(128, 3) decode_kernel(const __grid_constant__ 
 
 bool decode_eligible(const fkda_fwd_params& p) {
     return p.cu_seqlens == nullptr && p.T == 1 && (p.phase_mask == 0 || p.phase_mask == (FKDA_PHASE_PREPARE | FKDA_PHASE_RECURRENCE));
+}
+
+int launch_decode_ragged(const TwoPassArgs& a, cudaStream_t stream) {
+    const int64_t chains = a.N * a.H;
+    if (chains > 0x7fffffff) return FKDA_ERR_BAD_SHAPE;
+    decode_kernel<<<(unsigned)chains, 128, 0, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? FKDA_OK : FKDA_ERR_LAUNCH;
 }
 
 int launch_decode(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {

@@ -23,9 +23,10 @@ struct TwoPassArgs {
     uint8_t* workspace;    // [H][total_tiles] per-chunk records
     int32_t* queue;        // header word 0: tail / queue ticket counter of the persistent recurrence (zeroed per call)
     int32_t* status;       // header word 1: device status, 0 ok, else the code of a bounded wait that gave up
-    int32_t* short_flag;   // header word 8, or null: written by the prefix kernel of a ragged batch, 1 when no sequence is
-                           // longer than one chunk; the fused short-sequence kernel then serves the call and the general
-                           // kernels, enqueued behind it, return at once (0: the other way round)
+    int32_t* short_flag;   // header word 8, or null: written by the prefix kernel of a ragged batch that MAY consist of
+                           // one-chunk sequences; the kernels that can serve the call are all enqueued and all but one
+                           // return at once: 2 = every sequence has exactly one token (decode kernel), 1 = no sequence is
+                           // longer than one chunk (fused short-sequence kernel), 0 = the general kernels
                            // (header words 2, 3: push counter and finished-chain counter of the segment queue;
                            //  words 4..6: claim counters of the three layers of first segments)
     int32_t* qslots;       // segment queue: slot i receives the i-th pushed item (-1 = not yet pushed)
@@ -74,12 +75,13 @@ int launch_short(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches)
 // the prefix kernel decides on the device), and the launch of the fused kernel behind that decision.
 bool short_ragged_candidate(const fkda_fwd_params& p);
 int launch_short_ragged(const TwoPassArgs& a, cudaStream_t stream);
+int launch_decode_ragged(const TwoPassArgs& a, cudaStream_t stream);   // as many tokens as sequences: maybe one each
 
 // Fills the kernel arguments common to both implementations (pointers, strides, gate scale,
 // workspace carving).
 void fill_args(const fkda_fwd_params& p, TwoPassArgs* a);
 void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
-                        int cs_tokens, int32_t* short_flag, cudaStream_t stream);
+                        int cs_tokens, int32_t* short_flag, bool decode_enqueued, cudaStream_t stream);
 // First state-export slot of sequence n.
 __device__ __forceinline__ int64_t cs_first_slot(const TwoPassArgs& a, int64_t n) {
     if (a.cu_seqlens != nullptr) return a.cs_prefix[n];

@@ -50,8 +50,9 @@ __global__ void __launch_bounds__(128, 3) short_kernel(const __grid_constant__ T
     uint8_t* recs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(short_smem) + 15) & ~(uintptr_t)15);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, tq = lane & 3;
-    // a ragged batch: the prefix kernel found a sequence longer than one chunk, the general kernels serve the call
-    if (a.short_flag != nullptr && *a.short_flag == 0) return;
+    // a ragged batch that the prefix kernel has given to other kernels (a longer sequence: the general ones; one token
+    // each: the decode kernel)
+    if (a.short_flag != nullptr && *a.short_flag != 1) return;
     const int64_t n_chains = a.N * a.H;
     const int64_t chain0 = (int64_t)blockIdx.x * kShortChainsPerCta;
     const int row0 = warp * 32 + g;           // my rows: row0 + 16 mt + 8 hi

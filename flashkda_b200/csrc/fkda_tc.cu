@@ -423,10 +423,16 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     // A ragged batch whose sequences MAY all fit one chunk (the host sees only the totals): the prefix kernel decides,
     // the fused short-sequence kernel and the general kernels are both enqueued and one side returns at once.
     if (short_ragged_candidate(p) && !(p.flags & FKDA_FLAG_NO_SHORT)) a.short_flag = a.queue + 8;
+    // as many tokens as sequences: they may have one token each, the decode kernel's case
+    const bool try_decode = a.short_flag != nullptr && T_total == p.N && !(p.flags & FKDA_FLAG_NO_DECODE);
     if (varlen && do_prep) {
         launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order),
                            a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every,
-                           a.short_flag, stream);
+                           a.short_flag, try_decode, stream);
+        ++launches;
+    }
+    if (try_decode) {
+        if (launch_decode_ragged(a, stream) != FKDA_OK) return FKDA_ERR_LAUNCH;
         ++launches;
     }
     if (a.short_flag != nullptr) {

@@ -22,7 +22,7 @@ namespace fkda {
 __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __restrict__ cu, int64_t N,
                                                            int32_t* __restrict__ prefix, int32_t* __restrict__ order,
                                                            int32_t* __restrict__ cs_prefix, int cs_tokens,
-                                                           int32_t* __restrict__ short_flag) {
+                                                           int32_t* __restrict__ short_flag, int decode_enqueued) {
     __shared__ int64_t part[1024];
     const int tid = threadIdx.x;
     const int64_t per = (N + 1023) / 1024;
@@ -55,11 +55,16 @@ __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __rest
     };
     scan(kChunk, prefix);
     if (cs_prefix != nullptr) scan(cs_tokens, cs_prefix);
-    if (short_flag != nullptr) {   // 1 when no sequence is longer than one chunk
-        int longer = 0;
-        for (int64_t n = lo; n < hi; ++n) longer |= (cu[n + 1] - cu[n] > kChunk) ? 1 : 0;
+    if (short_flag != nullptr) {   // who serves the call (see TwoPassArgs::short_flag)
+        int longer = 0, not_one = 0;
+        for (int64_t n = lo; n < hi; ++n) {
+            const int64_t len = cu[n + 1] - cu[n];
+            longer |= (len > kChunk) ? 1 : 0;
+            not_one |= (len != 1) ? 1 : 0;
+        }
         longer = __syncthreads_or(longer);
-        if (tid == 0) *short_flag = longer ? 0 : 1;
+        not_one = __syncthreads_or(not_one);
+        if (tid == 0) *short_flag = longer ? 0 : ((decode_enqueued && !not_one) ? 2 : 1);
     }
     if (order != nullptr) {
         for (int64_t n = tid; n < N; n += 1024) {
@@ -233,8 +238,9 @@ __global__ void __launch_bounds__(128) recurrence_kernel(TwoPassArgs a) {
 // host launcher
 // ---------------------------------------------------------------------------------
 void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
-                        int cs_tokens, int32_t* short_flag, cudaStream_t stream) {
-    tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix, seq_order, cs_prefix, cs_tokens, short_flag);
+                        int cs_tokens, int32_t* short_flag, bool decode_enqueued, cudaStream_t stream) {
+    tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix, seq_order, cs_prefix, cs_tokens, short_flag,
+                                               decode_enqueued ? 1 : 0);
 }
 
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
@@ -296,7 +302,7 @@ int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launche
     const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
     if (varlen && do_prep) {
         launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order),
-                           a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every, nullptr, stream);
+                           a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every, nullptr, false, stream);
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {

@@ -92,11 +92,20 @@ def test_ragged_short_batch_matches_general_path_and_oracle(kind, state_dtype):
     w = Workload("rs", 1, sum(lens), 2, state_in=state_dtype, state_out=state_dtype, lower_bound=-2.0, seq_lens=lens)
     inp = make_inputs(w, seed=21)
     out_s, hT_s, untouched = _run_ragged(inp)
-    assert flashkda_b200.last_launch_count() == 4   # prefix, fused kernel, and the two general kernels that return at once
-    assert untouched, "the fused kernel keeps no chunk records"
+    # prefix, fused kernel, and the two general kernels that return at once; as many tokens as sequences: the decode
+    # kernel is enqueued too, and serves the call when every sequence has one token
+    assert flashkda_b200.last_launch_count() == (5 if kind == "ones" else 4)
+    assert untouched, "neither one-kernel path keeps chunk records"
     out_g, hT_g, untouched_g = _run_ragged(inp, flags=_lib.FLAG_NO_SHORT)
     assert flashkda_b200.last_launch_count() == 3 and not untouched_g
-    assert torch.equal(out_s, out_g) and torch.equal(hT_s, hT_g)
+    if kind == "ones":   # the decode kernel sums its dot products in another order (see test_decode.py)
+        assert oracle.err_ratio(out_g, out_s) <= 2e-3 and (out_s != out_g).float().mean().item() <= 0.05
+        assert oracle.err_ratio(hT_g, hT_s) <= 1e-3
+        out_f, hT_f, _ = _run_ragged(inp, flags=_lib.FLAG_NO_DECODE)   # the fused short-sequence kernel instead
+        assert flashkda_b200.last_launch_count() == 4
+        assert torch.equal(out_f, out_g) and torch.equal(hT_f, hT_g)
+    else:
+        assert torch.equal(out_s, out_g) and torch.equal(hT_s, hT_g)
     ref_out, ref_hT = run_oracle(inp)
     check_against(out_s, hT_s, ref_out, ref_hT)
     for n, L in enumerate(lens):
@@ -127,3 +136,30 @@ def test_ragged_short_batch_without_states_and_many_chains():
     assert torch.equal(out_s, out_g)
     ref_out, _ = run_oracle(inp)
     check_against(out_s, None, ref_out, None)
+
+
+def test_ragged_batch_with_as_many_tokens_as_sequences_but_not_one_each():
+    lens = [0, 2] * 20 + [1] * 8   # 48 tokens, 48 sequences: the decode kernel is enqueued and must stand back
+    w = Workload("rd", 1, sum(lens), 2, state_in="bf16", state_out="bf16", lower_bound=-2.0, seq_lens=lens)
+    inp = make_inputs(w, seed=24)
+    out_s, hT_s, untouched = _run_ragged(inp)
+    assert flashkda_b200.last_launch_count() == 5 and untouched
+    out_g, hT_g, _ = _run_ragged(inp, flags=_lib.FLAG_NO_SHORT)
+    assert torch.equal(out_s, out_g) and torch.equal(hT_s, hT_g)
+
+
+def test_ragged_decode_step_matches_the_fixed_batch_decode_step():
+    """cu_seqlens = 0, 1, 2, ... describes the same problem as a fixed batch with T = 1."""
+    N, H = 40, 4
+    w = Workload("rdf", N, 1, H, state_in="fp32", state_out="fp32", lower_bound=-2.0)
+    inp = make_inputs(w, seed=25)
+    out_f, hT_f = run_gpu(inp, "tc")
+    assert flashkda_b200.last_launch_count() == 1
+    rag = dict(inp)
+    for k in ("q", "k", "v", "g", "beta", "out"):
+        rag[k] = inp[k].reshape(1, N, *inp[k].shape[2:]).clone()
+    rag["cu_seqlens"] = torch.arange(N + 1, dtype=torch.int64)
+    rag["final_state"] = torch.zeros_like(inp["final_state"])
+    out_r, hT_r, untouched = _run_ragged(rag)
+    assert flashkda_b200.last_launch_count() == 5 and untouched
+    assert torch.equal(out_r.reshape(out_f.shape), out_f) and torch.equal(hT_r, hT_f)
