@@ -33,7 +33,7 @@ namespace fkda {
 using namespace sm100;
 
 constexpr int kTcChains = 3;    // chains (warpgroups) per CTA
-constexpr int kTcStages = 2;    // chunk records in flight per chain
+constexpr int kTcStages = 3;    // chunk records in flight per chain
 constexpr int kTcTmemCols = 512;
 constexpr int kTcStageBytes = kTcRecord;   // one chunk record per stage
 

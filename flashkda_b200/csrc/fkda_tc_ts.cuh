@@ -24,7 +24,7 @@ namespace fkda {
 
 // byte offsets inside one chain's shared-memory block (no state tile)
 constexpr int kTsStage = 0;                                   // kTcStages chunk records
-constexpr int kTsV = kTsStage + kTcStages * kTcStageBytes;    // kTcStages value tiles [16][128] bf16
+constexpr int kTsV = (kTsStage + kTcStages * kTcStageBytes + 127) / 128 * 128;   // kTcStages value tiles [16][128] bf16
 constexpr int kTsOut = kTsV + kTcStages * 4096;               // out tile [16][128] bf16
 constexpr int kTsChainBytes = kTsOut + 4096;
 static_assert(kTsV % 128 == 0 && kTsChainBytes % 128 == 0, "TMA tiles are 128-byte aligned");
@@ -77,7 +77,7 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
 
     const int bar_id = 1 + wg;
     const int64_t n_chains = a.N * a.H;
-    uint32_t full_phase[kTcStages] = {0, 0};
+    uint32_t full_bits = 0;   // bit s = phase of full[wg][s]
     uint32_t mma_phase = 0;
     bool failed = false;
     bool first_claim = true;
@@ -169,8 +169,8 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
                     dst[i] = make_uint4(sreg[4 * i], sreg[4 * i + 1], sreg[4 * i + 2], sreg[4 * i + 3]);
             }
             // ---- operands of chunk t have landed ----
-            if (!mbar_wait_bounded(&ctl.full[wg][s], full_phase[s], abort_flag, a.wait_ns)) { failed = true; break; }
-            full_phase[s] ^= 1u;
+            if (!mbar_wait_bounded(&ctl.full[wg][s], (full_bits >> s) & 1u, abort_flag, a.wait_ns)) { failed = true; break; }
+            full_bits ^= 1u << s;
 
             // ---- MMA1: D1[V,32] = S . [kd; qd]^T, A = the state copy in tensor memory (8 columns per K step) ----
             if (wiw == 0) {
