@@ -115,11 +115,18 @@ enum {
  * (csrc/flash_kda.cpp:5-26): same arguments plus the implementation selector. */
 size_t fkda_workspace_bytes(int64_t T_total, int64_t H, int64_t N, int32_t algo);
 
-/* Scratch bytes THIS call needs (<= fkda_workspace_bytes for the same totals): a decode step (fixed batch,
- * T == 1) needs only the 256-byte header, other calls their records and queue.  No counterpart in the reference. */
+/* Scratch bytes THIS call needs (<= fkda_workspace_bytes for the same totals): a fixed batch with at most 16 tokens
+ * per sequence (a decode step, T == 1, or a short step, T <= 16) needs only the 256-byte header, other calls their
+ * records and queue.  No counterpart in the reference. */
 size_t fkda_workspace_bytes_for(const fkda_fwd_params* p);
 
-/* Enqueues the forward pass on `stream` (a cudaStream_t passed as void*). */
+/* Enqueues the forward pass on `stream` (a cudaStream_t passed as void*).
+ * Paths: a fixed batch with T == 1 is one state read-modify-write kernel, with 2 <= T <= 16 one fused kernel, anything
+ * else the prepare kernel plus the tensor-core recurrence.  For a ragged batch (cu_seqlens) the host knows only the
+ * totals: when there are at most 16 tokens per sequence on average (and at least 64 (sequence, head) pairs), a prefix
+ * kernel decides on the device whether every sequence has one token, or at most 16, and the kernels of the paths that
+ * may apply are all enqueued; those that are not needed return at once.  Results do not depend on the path
+ * (the one-token kernel: to the summation order of its dot products). */
 int fkda_fwd(const fkda_fwd_params* p, void* stream);
 
 /* Synchronises `stream`, then reads the device status word that the kernels of the last call
