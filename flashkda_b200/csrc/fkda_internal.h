@@ -81,7 +81,8 @@ int launch_decode_ragged(const TwoPassArgs& a, cudaStream_t stream);   // as man
 // workspace carving).
 void fill_args(const fkda_fwd_params& p, TwoPassArgs* a);
 void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
-                        int cs_tokens, int32_t* short_flag, bool decode_enqueued, cudaStream_t stream);
+                        int cs_tokens, int32_t* short_flag, bool decode_enqueued, int32_t* critical_chunks, int64_t heads,
+                        int chain_slots, cudaStream_t stream);
 // First state-export slot of sequence n.
 __device__ __forceinline__ int64_t cs_first_slot(const TwoPassArgs& a, int64_t n) {
     if (a.cu_seqlens != nullptr) return a.cs_prefix[n];

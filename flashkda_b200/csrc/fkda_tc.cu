@@ -428,7 +428,7 @@ int launch_tc(const fkda_fwd_params& p, cudaStream_t stream, int* n_launches) {
     if (varlen && do_prep) {
         launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order),
                            a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every,
-                           a.short_flag, try_decode, stream);
+                           a.short_flag, try_decode, a.qslots != nullptr ? a.queue + 9 : nullptr, p.H, sms * kTcChains, stream);
         ++launches;
     }
     if (try_decode) {

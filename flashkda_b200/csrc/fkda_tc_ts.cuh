@@ -96,7 +96,10 @@ recurrence_tc_ts_kernel(const __grid_constant__ TwoPassArgs a, const __grid_cons
         const int64_t n = ch.n, bos = ch.bos, seq_len = ch.seq_len;
         const int h = ch.h, n_chunks = ch.n_chunks;
         const int c0 = seg * a.seg_chunks;                                             // my chunk range
-        const int c1 = (a.seg_chunks > 0 && c0 + a.seg_chunks < n_chunks) ? c0 + a.seg_chunks : n_chunks;
+        // (header word 9: the length from which a chain of a ragged batch is on the critical path and walked in one piece;
+        //  0 for fixed batches, whose chains are all alike)
+        const int critical = a.queue[9];
+        const int c1 = (a.seg_chunks > 0 && !(critical > 0 && n_chunks >= critical) && c0 + a.seg_chunks < n_chunks) ? c0 + a.seg_chunks : n_chunks;
         const uint8_t* rec_base = ch.rec_base;
         // thread v owns state row v: element S[v][k] of this chain sits at st_base + k
         const int64_t st_base = ((n * a.H + h) * (int64_t)kD + v) * (int64_t)kD;

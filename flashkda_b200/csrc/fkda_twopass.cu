@@ -22,7 +22,8 @@ namespace fkda {
 __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __restrict__ cu, int64_t N,
                                                            int32_t* __restrict__ prefix, int32_t* __restrict__ order,
                                                            int32_t* __restrict__ cs_prefix, int cs_tokens,
-                                                           int32_t* __restrict__ short_flag, int decode_enqueued) {
+                                                           int32_t* __restrict__ short_flag, int decode_enqueued,
+                                                           int32_t* __restrict__ critical_chunks, int64_t heads, int chain_slots) {
     __shared__ int64_t part[1024];
     const int tid = threadIdx.x;
     const int64_t per = (N + 1023) / 1024;
@@ -54,6 +55,10 @@ __global__ void __launch_bounds__(1024) tile_prefix_kernel(const int64_t* __rest
         if (tid == 1023) out[N] = (int32_t)part[1023];
     };
     scan(kChunk, prefix);
+    // A chain at least as long as a chain slot's even share of the whole work is on the critical path from its first
+    // chunk: the recurrence walks it in one piece instead of in queued segments.
+    if (critical_chunks != nullptr && tid == 1023)
+        *critical_chunks = (int32_t)((heads * part[1023] + chain_slots - 1) / chain_slots);
     if (cs_prefix != nullptr) scan(cs_tokens, cs_prefix);
     if (short_flag != nullptr) {   // who serves the call (see TwoPassArgs::short_flag)
         int longer = 0, not_one = 0;
@@ -238,9 +243,10 @@ __global__ void __launch_bounds__(128) recurrence_kernel(TwoPassArgs a) {
 // host launcher
 // ---------------------------------------------------------------------------------
 void launch_tile_prefix(const int64_t* cu_seqlens, int64_t N, int32_t* prefix, int32_t* seq_order, int32_t* cs_prefix,
-                        int cs_tokens, int32_t* short_flag, bool decode_enqueued, cudaStream_t stream) {
+                        int cs_tokens, int32_t* short_flag, bool decode_enqueued, int32_t* critical_chunks, int64_t heads,
+                        int chain_slots, cudaStream_t stream) {
     tile_prefix_kernel<<<1, 1024, 0, stream>>>(cu_seqlens, N, prefix, seq_order, cs_prefix, cs_tokens, short_flag,
-                                               decode_enqueued ? 1 : 0);
+                                               decode_enqueued ? 1 : 0, critical_chunks, heads, chain_slots);
 }
 
 size_t twopass_workspace_bytes(int64_t T_total, int64_t H, int64_t N) {
@@ -302,7 +308,7 @@ int launch_twopass(const fkda_fwd_params& p, cudaStream_t stream, int* n_launche
     const bool do_rec = p.phase_mask == 0 || (p.phase_mask & FKDA_PHASE_RECURRENCE);
     if (varlen && do_prep) {
         launch_tile_prefix(p.cu_seqlens, p.N, a.tile_prefix, const_cast<int32_t*>(a.seq_order),
-                           a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every, nullptr, false, stream);
+                           a.chunk_states != nullptr ? const_cast<int32_t*>(a.cs_prefix) : nullptr, 16 * a.cs_every, nullptr, false, nullptr, 0, 1, stream);
         ++launches;
     }
     if (a.total_tiles > 0 && do_prep) {
