@@ -67,6 +67,8 @@ def lib():
         L.fkda_noalloc_scratch_bytes.restype = ctypes.c_size_t
         L.fkda_device_status.restype = ctypes.c_int
         L.fkda_device_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        L.fkda_cp_fold.restype = ctypes.c_int
+        L.fkda_cp_fold.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int64, ctypes.c_void_p]
         _lib = L
     return _lib
 

@@ -64,11 +64,30 @@ def shard_maps(fwd_fn: Callable, q, k, v, g, beta, scale, A_log, dt_bias, lower_
     return M, N
 
 
+def fold(S: torch.Tensor, M: torch.Tensor, N: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``S . M + N`` over the leading dimensions of fp32 ``[..., 128, 128]`` tensors: a state through a shard's map.
+    On the device this is the library's own kernel (``fkda_cp_fold``: fp32 FMAs in a fixed order); host tensors
+    (the CPU tests, which run the oracle as operator) go through ``torch.matmul``."""
+    if not S.is_cuda:
+        R = torch.matmul(S, M)
+        return R if N is None else R + N
+    from . import _lib
+    S, M = S.contiguous(), M.contiguous()
+    N = None if N is None else N.contiguous()
+    assert S.dtype == M.dtype == torch.float32 and S.shape == M.shape and S.shape[-2:] == (D, D)
+    out = torch.empty_like(S)
+    rc = _lib.lib().fkda_cp_fold(S.data_ptr(), M.data_ptr(), None if N is None else N.data_ptr(), out.data_ptr(),
+                                 S.numel() // (D * D), torch.cuda.current_stream(S.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"fkda_cp_fold failed: {_lib.status_string(rc)}")
+    return out
+
+
 def fold_initial_state(first_end_state: torch.Tensor, maps: List[Tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
     """State entering the shard that follows rank 0 and the shards of ``maps`` (in order)."""
     S = first_end_state.to(torch.float32)
     for M, N in maps:
-        S = torch.matmul(S, M) + N
+        S = fold(S, M, N)
     return S
 
 
@@ -261,8 +280,8 @@ class SequenceSplit:
             return None, None
         Mt, Nt = self.M[0:1], self.N[0:1]
         for p in range(1, P):
-            Nt = torch.matmul(Nt, self.M[p:p + 1]) + self.N[p:p + 1]
-            Mt = torch.matmul(Mt, self.M[p:p + 1])
+            Nt = fold(Nt, self.M[p:p + 1], self.N[p:p + 1])
+            Mt = fold(Mt, self.M[p:p + 1])
         return Mt, Nt
 
     def finish(self, initial_state=None, final_state=None):
@@ -277,7 +296,7 @@ class SequenceSplit:
         for p in range(P):
             h0[p] = S[0]
             if p + 1 < P:
-                S = torch.matmul(S, self.M[p:p + 1]) + self.N[p:p + 1]
+                S = fold(S, self.M[p:p + 1], self.N[p:p + 1])
         hT = torch.zeros(P, H, D, D, dtype=torch.float32, device=dev)
         self._fwd(self.t[2], h0, hT)
         if final_state is not None:

@@ -89,7 +89,7 @@ def fwd_fla_context_parallel(q, k, v, g, beta, scale, out, A_log, dt_bias, lower
         if pre > 0:
             S = gathered[rank - pre][1]
             for j in range(rank - pre + 1, rank):
-                S = torch.matmul(S, gathered[j][0]) + gathered[j][1]
+                S = cp.fold(S, gathered[j][0], gathered[j][1])
             h0[0] = S[0]
     # 4. my tokens, for real
     if n_local > 0:

@@ -181,6 +181,12 @@ const char* fkda_status_string(int status);
 /* Number of kernels the last successful fkda_fwd call on this thread launched. */
 int fkda_last_launch_count(void);
 
+/* Context parallelism (no counterpart in the reference, which has no multi-GPU path): a shard of chunks maps the state
+ * it receives to the state it leaves as S_out = S_in . M + N (S, N as [V,K], M as [K,K]).  This folds `count`
+ * independent [128,128] fp32 row-major matrices: out[i] = S[i] . M[i] + N[i] (N == NULL: no offset), plain fp32 FMAs in
+ * the order k = 0 .. 127.  `out` must not alias S or M.  Enqueued on `stream`. */
+int fkda_cp_fold(const float* S, const float* M, const float* N, float* out, int64_t count, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -164,3 +164,23 @@ def test_sequence_parallel_single_gpu(parts):
     assert oracle.max_abs(one_out, out) <= 2e-2
     assert oracle.err_ratio(one_out, out) <= 1e-2
     assert oracle.err_ratio(one_hT, hT) <= 1e-2
+
+
+@pytest.mark.gpu
+def test_fold_kernel_matches_matmul():
+    """The library's own fold (S . M + N per head, fp32 FMAs in a fixed order) against torch's fp32 matmul."""
+    g = torch.Generator().manual_seed(0)
+    S, M, N = (torch.randn(3, 5, 128, 128, generator=g).cuda() for _ in range(3))
+    M = M * 0.1
+    for off in (N, None):
+        got = cp.fold(S, M, off)
+        ref = torch.matmul(S.double(), M.double()) + (0 if off is None else off.double())
+        assert got.dtype == torch.float32 and got.shape == S.shape
+        assert (got.double() - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+    # an identity map leaves the state as it is, bit for bit
+    eye = torch.eye(128, device="cuda").expand(3, 5, 128, 128).contiguous()
+    assert torch.equal(cp.fold(S, eye), S)
+    # the C entry point refuses an output that aliases an input (every CTA reads whole rows of S and all of M)
+    from flashkda_b200 import _lib
+    rc = _lib.lib().fkda_cp_fold(S.data_ptr(), M.data_ptr(), None, S.data_ptr(), 15, torch.cuda.current_stream().cuda_stream)
+    assert rc == 2
